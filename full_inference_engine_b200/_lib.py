@@ -1,0 +1,147 @@
+"""ctypes binding of libb200q.so — the only bridge between Python and the CUDA kernels.
+
+Nothing but raw pointers, sizes, enums and the current CUDA stream crosses this boundary
+(see ``include/b200q.h``).  There is no CPU implementation behind it: if the library is
+missing or a call fails, an exception says so.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+PACKAGE_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PACKAGE_DIR, "lib", "libb200q.so")
+
+# enums of include/b200q.h
+F16, BF16, F32 = 0, 1, 2
+W4_REF_SPLIT_HALF_SYM, W4_ASYM_ZP_INT32 = 0, 1
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
+W8_SCALE_F16, W8_SCALE_F32 = 0, 1
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_WAIT = range(7)
+
+_DTYPES = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+
+_c_void_p, _c_int, _c_i64, _c_size = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+
+_SIGNATURES = {
+    "b200q_version": (_c_int, []),
+    "b200q_status_string": (ctypes.c_char_p, [_c_int]),
+    "b200q_launch_count": (ctypes.c_uint64, []),
+    "b200q_last_error": (ctypes.c_char_p, []),
+    "b200q_quantize_w8_per_channel": (_c_int, [_c_void_p, _c_int, _c_i64, _c_int, _c_int, _c_int,
+                                               _c_void_p, _c_void_p, _c_void_p]),
+    "b200q_quantize_w4_grouped": (_c_int, [_c_void_p, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_int,
+                                           _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
+    "b200q_w4_dequant": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                                  _c_void_p, _c_i64, _c_void_p]),
+    "b200q_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int]),
+    "b200q_workspace_status": (_c_int, [_c_void_p, _c_void_p]),
+    "b200q_w8a16_forward": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_void_p, _c_int,
+                                     _c_void_p, _c_void_p, _c_i64, _c_int, _c_int, _c_int,
+                                     _c_void_p, _c_size, _c_int, _c_void_p]),
+    "b200q_w4a16_forward": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_int, _c_void_p,
+                                     _c_void_p, _c_int, _c_void_p, _c_void_p, _c_i64, _c_int, _c_int,
+                                     _c_int, _c_void_p, _c_size, _c_int, _c_void_p]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+class B200QError(RuntimeError):
+    """A libb200q call returned a non-zero status."""
+
+    def __init__(self, status: int, where: str):
+        lib = library()
+        text = lib.b200q_status_string(status).decode()
+        detail = lib.b200q_last_error().decode()
+        super().__init__(f"{where}: {text}" + (f" ({detail})" if detail else ""))
+        self.status = status
+
+
+def exported_symbols() -> list[str]:
+    """Every entry point ``include/b200q.h`` declares."""
+    return list(_SIGNATURES)
+
+
+def library() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with "
+                        "`python -m full_inference_engine_b200.build` (needs nvcc). "
+                        "This package has no CPU or PyTorch fallback for its kernels.")
+                lib = ctypes.CDLL(LIB_PATH)
+                for name, (restype, argtypes) in _SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.restype = restype
+                    fn.argtypes = argtypes
+                _lib = lib
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise B200QError(status, where)
+
+
+def dtype_enum(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dtype}") from None
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(tensor: torch.Tensor, what: str) -> None:
+    if tensor.device.type != "cuda":
+        raise RuntimeError(
+            f"{what} must be a CUDA tensor: the B200 kernels have no CPU path "
+            "(use reference_mode / unpack_w4_reference for the torch arithmetic)")
+
+
+# ------------------------------------------------------------------ workspace
+# One zero-initialised buffer per device (the reference keeps its dequantise scratch the
+# same way, engine/quantization/w4a16.py:59-76): split-K partials, tile counters and the
+# status word.  Calls on one device are expected to be stream-ordered with one another, as
+# they are under the reference's single worker thread; calls that overlap on the GPU from
+# different streams would share the counters.  Grown only by allocating a larger buffer;
+# earlier buffers stay alive because captured graphs may hold their addresses.
+_WORKSPACES: dict[int, torch.Tensor] = {}
+_RETIRED: list[torch.Tensor] = []
+_GRANULE = 8 << 20
+
+
+def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                "the b200q workspace would have to grow during CUDA-graph capture: run the "
+                "same call once eagerly on this device before capturing")
+        size = max(_GRANULE, (nbytes + _GRANULE - 1) // _GRANULE * _GRANULE)
+        if buf is not None:
+            _RETIRED.append(buf)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def workspace_bytes(fmt: int, m: int, n: int, k: int) -> int:
+    return int(library().b200q_workspace_bytes(fmt, m, n, k))
+
+
+def launch_count() -> int:
+    return int(library().b200q_launch_count())

@@ -1,0 +1,170 @@
+// The C ABI of libb200q: argument validation, kernel selection, bookkeeping.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "internal.cuh"
+
+namespace b200q {
+
+static std::atomic<uint64_t> g_launches{0};
+static thread_local char g_last_error[256] = "";
+
+void set_last_error_text(const char* text) {
+  std::snprintf(g_last_error, sizeof(g_last_error), "%s", text);
+}
+void set_last_error(const char* what, cudaError_t e) {
+  std::snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+}
+
+int note_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("kernel launch", e);
+    return B200Q_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200Q_OK;
+}
+
+// Rows of decode width go to the CUDA-core kernel: it needs no workspace, no
+// tensor maps and no TMEM, and at M <= 2 its arithmetic fits under the weight
+// stream.  Everything wider is a contraction and belongs on the tensor cores.
+constexpr int kSimtMaxRows = 2;
+
+static int run_forward(const ForwardArgs& a, int kernel) {
+  if (kernel == B200Q_KERNEL_SIMT) return launch_forward_simt(a);
+  if (kernel == B200Q_KERNEL_TC) return launch_forward_tc(a);
+  if (kernel != B200Q_KERNEL_AUTO) return B200Q_ERR_INVALID;
+  if (a.M <= kSimtMaxRows || !tc_supported(a)) return launch_forward_simt(a);
+  return launch_forward_tc(a);
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_version(void) { return 100; }
+
+const char* b200q_status_string(int status) {
+  switch (status) {
+    case B200Q_OK: return "ok";
+    case B200Q_ERR_INVALID: return "invalid argument";
+    case B200Q_ERR_UNSUPPORTED: return "unsupported geometry for this kernel";
+    case B200Q_ERR_ALIGNMENT: return "pointer or leading dimension is not 16-byte aligned";
+    case B200Q_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200Q_ERR_CUDA: return "CUDA call failed";
+    case B200Q_ERR_DEVICE_WAIT: return "a bounded device-side wait expired";
+    default: return "unknown status";
+  }
+}
+
+uint64_t b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* b200q_last_error(void) { return g_last_error; }
+
+int b200q_quantize_w8_per_channel(const void* w, int w_dtype, int64_t ldw, int N, int K, int mode,
+                                  int8_t* q, void* scales, void* stream) {
+  if (!w || !q || !scales || N < 0 || K <= 0 || ldw < K) return B200Q_ERR_INVALID;
+  if (mode != B200Q_W8_SCALE_F16 && mode != B200Q_W8_SCALE_F32) return B200Q_ERR_INVALID;
+  if (N == 0) return B200Q_OK;
+  return launch_quantize_w8(w, w_dtype, ldw, N, K, mode, q, scales, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_quantize_w4_grouped(const void* w, int w_dtype, int64_t ldw, int N, int K, int group,
+                              int layout, void* packed, void* scales, void* zeros, void* stream) {
+  if (!w || !packed || !scales || N < 0 || K <= 0 || ldw < K) return B200Q_ERR_INVALID;
+  if (group <= 0 || (group & 1) || K % group) return B200Q_ERR_INVALID;
+  if (layout == B200Q_W4_REF_SPLIT_HALF_SYM) {
+    if (zeros) return B200Q_ERR_INVALID;
+  } else if (layout == B200Q_W4_ASYM_ZP_INT32) {
+    if (!zeros || group % 8) return B200Q_ERR_INVALID;
+  } else {
+    return B200Q_ERR_INVALID;
+  }
+  if (N == 0) return B200Q_OK;
+  return launch_quantize_w4(w, w_dtype, ldw, N, K, group, layout, packed, scales, zeros,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b200q_w4_dequant(const void* packed, const void* scales, const void* zeros, int layout, int N,
+                     int K, int group, void* out, int64_t ldo, void* stream) {
+  if (!packed || !scales || !out || N < 0 || K <= 0 || ldo < K) return B200Q_ERR_INVALID;
+  if (group <= 0 || (group & 1) || K % group) return B200Q_ERR_INVALID;
+  if (layout == B200Q_W4_ASYM_ZP_INT32 && !zeros) return B200Q_ERR_INVALID;
+  if (layout != B200Q_W4_ASYM_ZP_INT32 && layout != B200Q_W4_REF_SPLIT_HALF_SYM)
+    return B200Q_ERR_INVALID;
+  if (N == 0) return B200Q_OK;
+  return launch_dequant_w4(packed, scales, zeros, layout, N, K, group, out, ldo,
+                           static_cast<cudaStream_t>(stream));
+}
+
+size_t b200q_workspace_bytes(int format, int M, int N, int K) {
+  if (format != 8 && format != 4) return 0;
+  return tc_workspace_bytes(format == 8 ? FMT_W8 : FMT_W4_REF, M, N, K);
+}
+
+int b200q_workspace_status(const void* workspace, void* stream) {
+  if (!workspace) return B200Q_ERR_INVALID;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    set_last_error("b200q_workspace_status", e);
+    return B200Q_ERR_CUDA;
+  }
+  return word == 0 ? B200Q_OK : B200Q_ERR_DEVICE_WAIT;
+}
+
+int b200q_w8a16_forward(const void* x, int64_t ldx, int act_dtype, const int8_t* qweight,
+                        int64_t ldw, const void* scales, int scale_dtype, const void* bias,
+                        void* y, int64_t ldy, int M, int N, int K, void* workspace,
+                        size_t workspace_bytes, int kernel, void* stream) {
+  if (M < 0 || N < 0 || K <= 0) return B200Q_ERR_INVALID;
+  if (M == 0 || N == 0) return B200Q_OK;
+  if (!x || !qweight || !scales || !y) return B200Q_ERR_INVALID;
+  if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
+  if (ldx < K || ldw < K || ldy < N) return B200Q_ERR_INVALID;
+  if (K % 16) return B200Q_ERR_UNSUPPORTED;
+  ForwardArgs a{};
+  a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
+  a.w = qweight; a.ldw = ldw; a.format = FMT_W8;
+  a.scales = scales; a.scale_dtype = scale_dtype; a.zeros = nullptr; a.group = 0;
+  a.bias = bias; a.y = y; a.ldy = ldy; a.M = M; a.N = N; a.K = K;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_forward(a, kernel);
+}
+
+int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype, const void* packed, int64_t ldw,
+                        int layout, const void* scales, const void* zeros, int group,
+                        const void* bias, void* y, int64_t ldy, int M, int N, int K,
+                        void* workspace, size_t workspace_bytes, int kernel, void* stream) {
+  if (M < 0 || N < 0 || K <= 0) return B200Q_ERR_INVALID;
+  if (M == 0 || N == 0) return B200Q_OK;
+  if (!x || !packed || !scales || !y) return B200Q_ERR_INVALID;
+  if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (layout == B200Q_W4_ASYM_ZP_INT32) {
+    if (!zeros) return B200Q_ERR_INVALID;
+  } else if (layout != B200Q_W4_REF_SPLIT_HALF_SYM) {
+    return B200Q_ERR_INVALID;
+  }
+  if (group <= 0 || K % group) return B200Q_ERR_INVALID;
+  if (group % 32) return B200Q_ERR_UNSUPPORTED;
+  if (ldx < K || ldw < K / 2 || ldy < N) return B200Q_ERR_INVALID;
+  ForwardArgs a{};
+  a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
+  a.w = packed; a.ldw = ldw;
+  a.format = layout == B200Q_W4_ASYM_ZP_INT32 ? FMT_W4_ASYM : FMT_W4_REF;
+  a.scales = scales; a.scale_dtype = B200Q_F16; a.zeros = zeros; a.group = group;
+  a.bias = bias; a.y = y; a.ldy = ldy; a.M = M; a.N = N; a.K = K;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_forward(a, kernel);
+}
+
+}  // extern "C"

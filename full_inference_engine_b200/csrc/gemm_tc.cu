@@ -1,0 +1,673 @@
+// Tensor-core weight-only linear for sm_100a: tcgen05.mma with the WEIGHTS on
+// the M side of the MMA and the tokens on the N side.
+//
+//   D[128 channels, TOK tokens] (fp32, TMEM) += Wd[128, 16] * X[TOK, 16]^T
+//
+// so a tile never pads the token count to 128: TOK is any multiple of 16 up to
+// 256 and is chosen per call.  One block owns 128 output channels x TOK tokens
+// x a K range (split-K over blockIdx.z when there are too few tiles to fill
+// the GPU).
+//
+// Warp roles (320 threads):
+//   warp 0     TMA producer: packed weights [128 x 64 B] boxes (no swizzle) and
+//              activation boxes [TOK x 64 elements] (128-byte swizzle)
+//   warp 1     TMEM allocation, tcgen05.mma issue (one elected thread), commits
+//   warps 2-9  dequantise the packed stage out of shared memory into the
+//              128-byte-swizzled K-major A operand stage, later the epilogue:
+//              tcgen05.ld, scale/bias, store (or split-K partials + last block
+//              reduces, counters reset for the next launch)
+//
+// Three rings step once per 128-wide K block: packed weights (P), dequantised
+// A operand (two 64-wide swizzle atoms) and activations (X, two atoms).
+//
+// Reference counterparts: _w4a16_linear_kernel (engine/kernels/w4a16_linear.py:27-74),
+// _w8a16_linear_kernel (engine/kernels/w8a16_linear.py:10-40) and the dense
+// dequantise-then-cuBLAS branch of W4A16Linear (engine/quantization/w4a16.py:158-178).
+#include <mutex>
+#include <unordered_map>
+
+#include "internal.cuh"
+#include "ptx.cuh"
+
+namespace b200q {
+
+constexpr int kTcThreads = 320;
+constexpr int kDequantThreads = 256;
+constexpr int kDequantWarps = 8;
+constexpr int kBlockN = 128;                 // output channels per block (UMMA M)
+constexpr int kBlockK = 128;                 // K elements per pipeline step
+constexpr int kAtomBytesA = kBlockN * 128;   // one 64-wide K atom of the A operand: 16 KB
+constexpr int kStageBytesA = 2 * kAtomBytesA;
+constexpr int kMaxRing = 8;
+constexpr int kSmemBudget = 226 * 1024;      // dynamic shared memory we ask for at most
+
+struct TcParams {
+  const void* scales;
+  int scale_is_f32;
+  const __half* zeros;
+  const void* bias;
+  void* y;
+  int64_t ldy;
+  int M, N, K;
+  int groups;        // K / 128 for the 4-bit formats
+  int tok;           // tokens per tile
+  int tmem_cols;
+  uint32_t idesc;
+  int kb_total;      // ceil(K / 128)
+  int kb_per_split;
+  int splits;
+  int np, na, nx;    // ring depths
+  float* partial;    // [splits, M, N] fp32 (split-K only)
+  unsigned* counters;  // [m_tiles * n_tiles], zero between launches
+  unsigned* status;    // device status word (non-zero: a bounded wait expired)
+};
+
+template <int FMT>
+struct PackedStage {
+  // bytes of packed weights per K block of 128
+  static constexpr int kBytes = (FMT == FMT_W8) ? kBlockN * 128 : kBlockN * 64;
+};
+
+// Abort-aware bounded wait: gives up when the poll budget is spent or when
+// another role has already flagged the block as failed.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort) {
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 0x3FF) == 0x3FF && *abort) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void flag_failure(volatile int* abort, unsigned* status, unsigned code) {
+  *abort = 1;
+  atomicOr(status, code);
+}
+
+__device__ __forceinline__ uint32_t swizzled_chunk_offset(int row, int chunk) {
+  // 128-byte rows, 16-byte chunks XOR-ed with the row index inside each 8-row atom
+  return static_cast<uint32_t>((row >> 3) * 1024 + (row & 7) * 128 + (((chunk ^ (row & 7)) & 7) << 4));
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "r"(addr));
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_operand(__half2 h);
+template <>
+__device__ __forceinline__ uint32_t pack_operand<__half>(__half2 h) {
+  return as_u32(h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_operand<__nv_bfloat16>(__half2 h) {
+  return h2_to_bf162(h);   // fp16 dequant value, then rounded to bf16 (what .to(bf16) does)
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+template <int FMT, typename T>
+__global__ void __launch_bounds__(kTcThreads, 1)
+wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                  const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the swizzled operand tiles
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int x_stage_bytes = p.tok * 256;                 // two atoms of [tok x 128 B]
+  const uint32_t a_ring = smem_base;
+  const uint32_t x_ring = a_ring + p.na * kStageBytesA;
+  const uint32_t p_ring = x_ring + p.nx * x_stage_bytes;
+  const uint32_t bars = p_ring + p.np * PackedStage<FMT>::kBytes;
+  // barrier slots (8 bytes each)
+  const uint32_t p_full = bars;
+  const uint32_t p_empty = p_full + 8 * kMaxRing;
+  const uint32_t a_full = p_empty + 8 * kMaxRing;
+  const uint32_t a_empty = a_full + 8 * kMaxRing;
+  const uint32_t x_full = a_empty + 8 * kMaxRing;
+  const uint32_t x_empty = x_full + 8 * kMaxRing;
+  const uint32_t acc_full = x_empty + 8 * kMaxRing;
+  const uint32_t tmem_slot = acc_full + 8;
+  const uint32_t abort_slot = tmem_slot + 4;
+  const uint32_t last_slot = abort_slot + 4;
+  uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_p =
+      reinterpret_cast<volatile uint32_t*>(generic_base + (tmem_slot - smem_base));
+  volatile int* abort_p = reinterpret_cast<volatile int*>(generic_base + (abort_slot - smem_base));
+  volatile int* last_p = reinterpret_cast<volatile int*>(generic_base + (last_slot - smem_base));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+  const int nkb = max(kb1 - kb0, 0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kMaxRing; ++i) {
+      mbar_init(p_full + 8 * i, 1);
+      mbar_init(p_empty + 8 * i, kDequantWarps);
+      mbar_init(a_full + 8 * i, kDequantWarps);
+      mbar_init(a_empty + 8 * i, 1);
+      mbar_init(x_full + 8 * i, 1);
+      mbar_init(x_empty + 8 * i, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_p = 0;
+    *last_p = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_p;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int kb = kb0 + i;
+        const int sp = i % p.np, sx = i % p.nx;
+        ok = wait_or_abort(p_empty + 8 * sp, ((i / p.np) & 1) ^ 1, abort_p);
+        if (!ok) break;
+        const uint32_t pdst = p_ring + sp * PackedStage<FMT>::kBytes;
+        mbar_arrive_expect_tx(p_full + 8 * sp, PackedStage<FMT>::kBytes);
+        if (FMT == FMT_W8) {
+          tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 128, n_tile * kBlockN);
+          tma_load_2d(pdst + kBlockN * 64, &tm_w, p_full + 8 * sp, kb * 128 + 64, n_tile * kBlockN);
+        } else {
+          tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 64, n_tile * kBlockN);
+        }
+        ok = wait_or_abort(x_empty + 8 * sx, ((i / p.nx) & 1) ^ 1, abort_p);
+        if (!ok) break;
+        const uint32_t xdst = x_ring + sx * x_stage_bytes;
+        mbar_arrive_expect_tx(x_full + 8 * sx, static_cast<uint32_t>(x_stage_bytes));
+        tma_load_2d(xdst, &tm_x, x_full + 8 * sx, kb * kBlockK, m_tile * p.tok);
+        tma_load_2d(xdst + p.tok * 128, &tm_x, x_full + 8 * sx, kb * kBlockK + 64, m_tile * p.tok);
+        issued = i + 1;
+      }
+      if (!ok) flag_failure(abort_p, p.status, 1u);
+      if (*abort_p) {
+        // let the copies already in flight land before the block's shared memory is released
+        for (int i = max(0, issued - kMaxRing); i < issued; ++i) {
+          if (i >= issued - p.np) mbar_wait(p_full + 8 * (i % p.np), (i / p.np) & 1);
+          if (i >= issued - p.nx) mbar_wait(x_full + 8 * (i % p.nx), (i / p.nx) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int sa = i % p.na, sx = i % p.nx;
+        ok = wait_or_abort(x_full + 8 * sx, (i / p.nx) & 1, abort_p) &&
+             wait_or_abort(a_full + 8 * sa, (i / p.na) & 1, abort_p);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t a_stage = a_ring + sa * kStageBytesA;
+        const uint32_t x_stage = x_ring + sx * x_stage_bytes;
+#pragma unroll
+        for (int atom = 0; atom < 2; ++atom) {
+          const uint64_t adesc = umma_desc_sw128(a_stage + atom * kAtomBytesA);
+          const uint64_t bdesc = umma_desc_sw128(x_stage + atom * p.tok * 128);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // advance 16 elements = 32 bytes along K inside the swizzle atom
+            umma_f16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc,
+                        (i > 0 || atom > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(x_empty + 8 * sx);
+        umma_commit(a_empty + 8 * sa);
+      }
+      if (!ok) flag_failure(abort_p, p.status, 2u);
+      umma_commit(acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------ dequant warps
+    const int td = threadIdx.x - 64;          // 0..255
+    const int q = td & 3;                      // 16-byte vector inside a 64-byte packed row
+    const int r_base = td >> 2;                // 0..63
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int kb = kb0 + i;
+      const int sp = i % p.np, sa = i % p.na;
+      // group parameters first: their latency hides behind the barrier waits
+      __half2 scale2[2];
+      __half2 bias_lo[2], nbias_hi[2];
+      if (FMT != FMT_W8) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n_tile * kBlockN + r_base + 64 * j;
+          __half s = __float2half_rn(0.0f);
+          float zp = 8.0f;
+          if (n < p.N) {
+            const int64_t si = static_cast<int64_t>(n) * p.groups + kb;
+            s = __ldg(reinterpret_cast<const __half*>(p.scales) + si);
+            if (FMT == FMT_W4_ASYM) zp = __half2float(__ldg(p.zeros + si));
+          }
+          scale2[j] = __half2half2(s);
+          bias_lo[j] = __float2half2_rn(1024.0f + zp);
+          nbias_hi[j] = __float2half2_rn(-(64.0f + zp));
+        }
+      }
+      ok = wait_or_abort(p_full + 8 * sp, (i / p.np) & 1, abort_p) &&
+           wait_or_abort(a_empty + 8 * sa, ((i / p.na) & 1) ^ 1, abort_p);
+      if (!ok) break;
+      const uint32_t p_stage = p_ring + sp * PackedStage<FMT>::kBytes;
+      const uint32_t a_stage = a_ring + sa * kStageBytesA;
+      if (FMT == FMT_W4_REF) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int row = r_base + 64 * j;
+          const uint4 v = ld_shared_v4(p_stage + (row * 4 + q) * 16);
+          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+          uint32_t lo[8], hi[8];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            W4Quad d = dequant_w4_word_splithalf(words[w], bias_lo[j], nbias_hi[j], scale2[j]);
+            lo[2 * w] = pack_operand<T>(d.lo01);
+            lo[2 * w + 1] = pack_operand<T>(d.lo23);
+            hi[2 * w] = pack_operand<T>(d.hi01);
+            hi[2 * w + 1] = pack_operand<T>(d.hi23);
+          }
+          // low nibbles: K offsets 16q..16q+15 of atom 0; high nibbles: same of atom 1
+          const uint32_t o0 = swizzled_chunk_offset(row, 2 * q);
+          const uint32_t o1 = swizzled_chunk_offset(row, 2 * q + 1);
+          st_shared_v4(a_stage + o0, lo[0], lo[1], lo[2], lo[3]);
+          st_shared_v4(a_stage + o1, lo[4], lo[5], lo[6], lo[7]);
+          st_shared_v4(a_stage + kAtomBytesA + o0, hi[0], hi[1], hi[2], hi[3]);
+          st_shared_v4(a_stage + kAtomBytesA + o1, hi[4], hi[5], hi[6], hi[7]);
+        }
+      } else if (FMT == FMT_W4_ASYM) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int row = r_base + 64 * j;
+          const uint4 v = ld_shared_v4(p_stage + (row * 4 + q) * 16);
+          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+          // 32 consecutive K: offsets 32q.. -> atom q/2, chunks 4(q%2)..4(q%2)+3
+          const uint32_t atom = a_stage + (q >> 1) * kAtomBytesA;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            W4Oct o = dequant_w4_word_seq(words[w], bias_lo[j], nbias_hi[j], scale2[j]);
+            st_shared_v4(atom + swizzled_chunk_offset(row, 4 * (q & 1) + w), pack_operand<T>(o.k01),
+                         pack_operand<T>(o.k23), pack_operand<T>(o.k45), pack_operand<T>(o.k67));
+          }
+        }
+      } else {
+        // W8: two [128 x 64 B] sub-tiles; sub-tile h holds K offsets 64h..64h+63
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int h = j >> 1;
+          const int row = r_base + 64 * (j & 1);
+          const uint4 v = ld_shared_v4(p_stage + h * (kBlockN * 64) + (row * 4 + q) * 16);
+          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+          uint32_t out[8];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            __half2 k01, k23;
+            int8x4_to_h2(words[w], k01, k23);
+            out[2 * w] = pack_operand<T>(k01);
+            out[2 * w + 1] = pack_operand<T>(k23);
+          }
+          const uint32_t atom = a_stage + h * kAtomBytesA;
+          st_shared_v4(atom + swizzled_chunk_offset(row, 2 * q), out[0], out[1], out[2], out[3]);
+          st_shared_v4(atom + swizzled_chunk_offset(row, 2 * q + 1), out[4], out[5], out[6], out[7]);
+        }
+      }
+      // make the generic-proxy writes visible to the tensor core (async proxy)
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(a_full + 8 * sa);
+        mbar_arrive(p_empty + 8 * sp);
+      }
+    }
+    if (!ok) flag_failure(abort_p, p.status, 4u);
+
+    // ------------------------------------------------------------ epilogue
+    bool acc_ok = wait_or_abort(acc_full, 0, abort_p);
+    if (!acc_ok) flag_failure(abort_p, p.status, 8u);
+    tc_fence_after_sync();
+    acc_ok = __all_sync(0xffffffffu, acc_ok && !*abort_p) != 0;
+    const int lane_quarter = warp & 3;                   // TMEM lanes this warp may read
+    const int col_half = (warp - 2) >> 2;                // which half of the token columns
+    const int n = n_tile * kBlockN + lane_quarter * 32 + lane;
+    const int half_cols = p.tok >> 1;
+    const int c_begin = col_half * half_cols;
+    const int m_base = m_tile * p.tok;
+    T* yT = static_cast<T*>(p.y);
+    float ch_scale = 1.0f, ch_bias = 0.0f;
+    if (n < p.N) {
+      if (FMT == FMT_W8)
+        ch_scale = p.scale_is_f32 ? reinterpret_cast<const float*>(p.scales)[n]
+                                  : __half2float(reinterpret_cast<const __half*>(p.scales)[n]);
+      if (p.bias != nullptr) ch_bias = static_cast<float>(static_cast<const T*>(p.bias)[n]);
+    }
+    if (acc_ok && nkb > 0) {
+      for (int c = 0; c < half_cols; c += 8) {
+        uint32_t r[8];
+        tmem_ld_x8(tmem_base + (static_cast<uint32_t>(lane_quarter * 32) << 16) + (c_begin + c), r);
+        tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int m = m_base + c_begin + c + j;
+            if (m < p.M) {
+              const float v = __uint_as_float(r[j]);
+              if (p.splits == 1) {
+                yT[static_cast<int64_t>(m) * p.ldy + n] = from_float<T>(v * ch_scale + ch_bias);
+              } else {
+                p.partial[(static_cast<int64_t>(split) * p.M + m) * p.N + n] = v;
+              }
+            }
+          }
+        }
+      }
+    }
+    if (p.splits > 1) {
+      // last block to arrive for this tile sums the partials in split order
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      unsigned* counter = p.counters + (m_tile * gridDim.x + n_tile);
+      if (td == 0) {
+        const unsigned prev = atomicAdd(counter, 1u);
+        *last_p = (prev == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      if (*last_p) {
+        __threadfence();
+        if (n < p.N) {
+          for (int c = 0; c < half_cols; ++c) {
+            const int m = m_base + c_begin + c;
+            if (m >= p.M) break;
+            float v = 0.0f;
+            for (int z = 0; z < p.splits; ++z)
+              v += __ldcg(p.partial + (static_cast<int64_t>(z) * p.M + m) * p.N + n);
+            yT[static_cast<int64_t>(m) * p.ldy + n] = from_float<T>(v * ch_scale + ch_bias);
+          }
+        }
+        if (td == 0) *counter = 0u;      // ready for the next launch / graph replay
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, ld;
+  uint32_t b0, b1, kind;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 &&
+           kind == o.kind;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.d0 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.d1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= (k.ld + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+    h ^= ((static_cast<uint64_t>(k.b0) << 32 | k.b1) + (h << 6) + (h >> 2));
+    h ^= k.kind;
+    return static_cast<size_t>(h);
+  }
+};
+
+// Tensor maps are pure functions of (pointer, shape, pitch, box): cache them.
+// Encoding is a host-only driver call, legal while a stream is capturing.
+static bool get_tensor_map(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, int elem_bytes,
+                           uint64_t d0, uint64_t d1, uint64_t ld_bytes, uint32_t b0, uint32_t b1,
+                           CUtensorMapSwizzle swz) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, d0, d1, ld_bytes, b0, b1, static_cast<uint32_t>(dt) * 16u + static_cast<uint32_t>(swz)};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_last_error_text("cuTensorMapEncodeTiled entry point not found");
+    return false;
+  }
+  cuuint64_t dims[2] = {d0, d1};
+  cuuint64_t strides[1] = {ld_bytes};
+  cuuint32_t box[2] = {b0, b1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  (void)elem_bytes;
+  if (r != CUDA_SUCCESS) {
+    set_last_error_text("cuTensorMapEncodeTiled failed");
+    return false;
+  }
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+struct TcPlan {
+  int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, tmem_cols;
+  size_t smem_bytes;
+};
+
+static int packed_stage_bytes(int format) { return format == FMT_W8 ? kBlockN * 128 : kBlockN * 64; }
+
+static TcPlan make_plan(int format, int M, int N, int K) {
+  TcPlan pl{};
+  const int mt = (M + 255) / 256;
+  int tok = ((M + mt - 1) / mt + 15) / 16 * 16;
+  if (tok < 16) tok = 16;
+  pl.tok = tok;
+  pl.m_tiles = (M + tok - 1) / tok;
+  pl.n_tiles = (N + kBlockN - 1) / kBlockN;
+  pl.kb_total = (K + kBlockK - 1) / kBlockK;
+  int cols = 32;
+  while (cols < tok) cols <<= 1;
+  pl.tmem_cols = cols;
+
+  // Ring depths.  Narrow token tiles are the HBM-bound regime: keep a block
+  // under half an SM's shared memory so two blocks are resident and one
+  // block's set-up and epilogue overlap the other's weight stream.
+  const int pbytes = packed_stage_bytes(format);
+  const int xbytes = tok * 256;
+  auto total = [&](int np, int na, int nx) {
+    return static_cast<size_t>(na) * kStageBytesA + static_cast<size_t>(nx) * xbytes +
+           static_cast<size_t>(np) * pbytes + 1024 /*alignment*/ + 8 * kMaxRing * 6 + 64;
+  };
+  const bool two_per_sm = tok <= 32;
+  const size_t budget = two_per_sm ? 112 * 1024 : static_cast<size_t>(kSmemBudget);
+  pl.na = 2;
+  pl.nx = 2;
+  pl.np = 2;
+  while (pl.np < (two_per_sm ? kMaxRing : 6) && total(pl.np + 1, pl.na, pl.nx) <= budget) ++pl.np;
+  if (!two_per_sm) {
+    while (pl.nx < 4 && total(pl.np, pl.na, pl.nx + 1) <= budget) ++pl.nx;
+    while (pl.na < 3 && total(pl.np, pl.na + 1, pl.nx) <= budget) ++pl.na;
+  }
+  pl.smem_bytes = total(pl.np, pl.na, pl.nx);
+
+  // split-K: choose the smallest split count that fills the resident slots well
+  const int tiles = pl.m_tiles * pl.n_tiles;
+  const int slots = 148 * (two_per_sm ? 2 : 1);
+  int max_splits = pl.kb_total / 4;          // at least four K blocks per split
+  if (max_splits > 16) max_splits = 16;
+  if (max_splits < 1) max_splits = 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= max_splits; ++s) {
+    const int ctas = tiles * s;
+    const int waves = (ctas + slots - 1) / slots;
+    const double eff = static_cast<double>(ctas) / (static_cast<double>(waves) * slots);
+    if (eff > best_eff + 0.05) {
+      best_eff = eff;
+      best = s;
+    }
+    if (eff >= 0.9) break;
+  }
+  if (tiles >= slots) best = 1;
+  pl.kb_per_split = (pl.kb_total + best - 1) / best;
+  pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
+  return pl;
+}
+
+size_t tc_workspace_bytes(int format, int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  TcPlan pl = make_plan(format, M, N, K);
+  // status word + counters always; partials only when split
+  size_t bytes = 256 + sizeof(unsigned) * static_cast<size_t>(pl.m_tiles) * pl.n_tiles;
+  bytes = (bytes + 255) / 256 * 256;
+  if (pl.splits > 1) bytes += sizeof(float) * static_cast<size_t>(pl.splits) * M * N;
+  return bytes;
+}
+
+bool tc_supported(const ForwardArgs& a) {
+  if (a.format != FMT_W8 && a.group != 128) return false;
+  if (a.format == FMT_W8 ? (a.K % 16 != 0) : (a.K % 128 != 0)) return false;
+  if (reinterpret_cast<uintptr_t>(a.x) % 16 || (a.ldx * 2) % 16) return false;
+  if (reinterpret_cast<uintptr_t>(a.w) % 16 || a.ldw % 16) return false;
+  return true;
+}
+
+template <int FMT, typename T>
+static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
+  static bool attr_set_dev[64] = {};
+  static std::mutex attr_mu;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    bool& attr_set = attr_set_dev[dev & 63];
+    std::lock_guard<std::mutex> g(attr_mu);
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(wq_gemm_tc_kernel<FMT, T>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+      if (e != cudaSuccess) {
+        set_last_error("cudaFuncSetAttribute", e);
+        return B200Q_ERR_CUDA;
+      }
+      attr_set = true;
+    }
+  }
+  CUtensorMap tm_w, tm_x;
+  const uint64_t w_cols = (FMT == FMT_W8) ? static_cast<uint64_t>(a.K) : static_cast<uint64_t>(a.K / 2);
+  if (!get_tensor_map(&tm_w, a.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_cols, static_cast<uint64_t>(a.N),
+                      static_cast<uint64_t>(a.ldw), 64, kBlockN, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return B200Q_ERR_CUDA;
+  const CUtensorMapDataType xdt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (!get_tensor_map(&tm_x, a.x, xdt, 2, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
+                      static_cast<uint64_t>(a.ldx) * 2, 64, static_cast<uint32_t>(pl.tok),
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return B200Q_ERR_CUDA;
+
+  TcParams p{};
+  p.scales = a.scales;
+  p.scale_is_f32 = a.scale_dtype == B200Q_F32;
+  p.zeros = static_cast<const __half*>(a.zeros);
+  p.bias = a.bias;
+  p.y = a.y;
+  p.ldy = a.ldy;
+  p.M = a.M;
+  p.N = a.N;
+  p.K = a.K;
+  p.groups = (FMT == FMT_W8) ? 1 : a.K / 128;
+  p.tok = pl.tok;
+  p.tmem_cols = pl.tmem_cols;
+  p.idesc = umma_idesc_f16(a.act_dtype == B200Q_F16 ? 0u : 1u, 128u, static_cast<uint32_t>(pl.tok));
+  p.kb_total = pl.kb_total;
+  p.kb_per_split = pl.kb_per_split;
+  p.splits = pl.splits;
+  p.np = pl.np;
+  p.na = pl.na;
+  p.nx = pl.nx;
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  p.status = reinterpret_cast<unsigned*>(ws);
+  p.counters = reinterpret_cast<unsigned*>(ws + 256);
+  size_t off = 256 + sizeof(unsigned) * static_cast<size_t>(pl.m_tiles) * pl.n_tiles;
+  off = (off + 255) / 256 * 256;
+  p.partial = reinterpret_cast<float*>(ws + off);
+
+  dim3 grid(pl.n_tiles, pl.m_tiles, pl.splits), block(kTcThreads);
+  wq_gemm_tc_kernel<FMT, T><<<grid, block, pl.smem_bytes, a.stream>>>(tm_w, tm_x, p);
+  return note_launch();
+}
+
+int launch_forward_tc(const ForwardArgs& a) {
+  if (a.M <= 0 || a.N <= 0) return B200Q_OK;
+  if (!tc_supported(a)) return B200Q_ERR_UNSUPPORTED;
+  const TcPlan pl = make_plan(a.format, a.M, a.N, a.K);
+  const size_t need = tc_workspace_bytes(a.format, a.M, a.N, a.K);
+  if (a.workspace == nullptr || a.workspace_bytes < need) return B200Q_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(a.workspace) % 256) return B200Q_ERR_ALIGNMENT;
+  const bool h = a.act_dtype == B200Q_F16;
+  switch (a.format) {
+    case FMT_W8:
+      return h ? launch_tc_typed<FMT_W8, __half>(a, pl) : launch_tc_typed<FMT_W8, __nv_bfloat16>(a, pl);
+    case FMT_W4_REF:
+      return h ? launch_tc_typed<FMT_W4_REF, __half>(a, pl)
+               : launch_tc_typed<FMT_W4_REF, __nv_bfloat16>(a, pl);
+    case FMT_W4_ASYM:
+      return h ? launch_tc_typed<FMT_W4_ASYM, __half>(a, pl)
+               : launch_tc_typed<FMT_W4_ASYM, __nv_bfloat16>(a, pl);
+    default:
+      return B200Q_ERR_INVALID;
+  }
+}
+
+}  // namespace b200q

@@ -1,0 +1,58 @@
+// Declarations shared by the translation units of libb200q.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200q.h"
+#include "convert.cuh"
+
+namespace b200q {
+
+enum Format { FMT_W8 = 0, FMT_W4_REF = 1, FMT_W4_ASYM = 2 };
+
+// Everything a forward kernel needs, format-agnostic.
+struct ForwardArgs {
+  const void* x;        // [M, ldx] activations (f16 / bf16)
+  int64_t ldx;          // elements
+  int act_dtype;        // B200Q_F16 / B200Q_BF16
+  const void* w;        // packed weights
+  int64_t ldw;          // BYTES per weight row
+  int format;           // Format
+  const void* scales;   // W8: [N] f16|f32; W4: [N, K/group] f16
+  int scale_dtype;      // W8 only
+  const void* zeros;    // W4 ASYM: [N, K/group] f16
+  int group;            // W4 only
+  const void* bias;     // [N] act dtype or null
+  void* y;              // [M, ldy]
+  int64_t ldy;          // elements
+  int M, N, K;
+  void* workspace;
+  size_t workspace_bytes;
+  cudaStream_t stream;
+};
+
+// Records a launch (and any launch error) — returns a b200q_status.
+int note_launch();
+void set_last_error(const char* what, cudaError_t e);
+void set_last_error_text(const char* text);
+
+// quantize.cu
+int launch_quantize_w8(const void* w, int w_dtype, int64_t ldw, int N, int K, int mode, int8_t* q,
+                       void* scales, cudaStream_t stream);
+int launch_quantize_w4(const void* w, int w_dtype, int64_t ldw, int N, int K, int group,
+                       int layout, void* packed, void* scales, void* zeros, cudaStream_t stream);
+int launch_dequant_w4(const void* packed, const void* scales, const void* zeros, int layout,
+                      int N, int K, int group, void* out, int64_t ldo, cudaStream_t stream);
+
+// gemv_simt.cu — CUDA-core path, any M (rows are processed four at a time).
+int launch_forward_simt(const ForwardArgs& a);
+
+// gemm_tc.cu — tcgen05 path.
+bool tc_supported(const ForwardArgs& a);
+size_t tc_workspace_bytes(int format, int M, int N, int K);
+int launch_forward_tc(const ForwardArgs& a);
+
+}  // namespace b200q

@@ -1,0 +1,179 @@
+/*
+ * b200q — weight-only quantized linear forward for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libb200q.so.  Plain pointers and sizes only: every pointer is a
+ * DEVICE pointer unless its comment says otherwise, `stream` is a
+ * cudaStream_t passed as void*, and every function returns a b200q_status
+ * (0 = ok).  Nothing here allocates device memory, synchronises the device
+ * or reads results back to the host, so every call may be recorded into a
+ * CUDA graph.
+ *
+ * Each entry point names the interface of the reference project
+ * (Vaibhav7711/full-inference-engine, paths relative to its root) that a
+ * binding would replace with it.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200q_status {
+  B200Q_OK = 0,
+  B200Q_ERR_INVALID = 1,      /* bad geometry, null pointer, unknown enum            */
+  B200Q_ERR_UNSUPPORTED = 2,  /* legal request this build has no kernel for          */
+  B200Q_ERR_ALIGNMENT = 3,    /* pointer or leading dimension not 16-byte aligned    */
+  B200Q_ERR_WORKSPACE = 4,    /* workspace missing or smaller than workspace_bytes() */
+  B200Q_ERR_CUDA = 5,         /* a CUDA runtime/driver call failed                   */
+  B200Q_ERR_DEVICE_WAIT = 6   /* a bounded device-side wait expired (status word)    */
+} b200q_status;
+
+/* element types of activations, outputs, scales and quantizer inputs */
+typedef enum b200q_dtype {
+  B200Q_F16 = 0,
+  B200Q_BF16 = 1,
+  B200Q_F32 = 2
+} b200q_dtype;
+
+/* INT4 container layouts */
+typedef enum b200q_w4_layout {
+  /* The reference layout (engine/kernels/w4a16_format.py:32-50): symmetric
+   * values in [-7,7] stored +8, two per uint8, split-half inside each group:
+   * byte j of a group holds input j (low nibble) and input j+G/2 (high
+   * nibble).  packed [N, K/2] uint8, scales [N, K/G] fp16, no zero-points. */
+  B200Q_W4_REF_SPLIT_HALF_SYM = 0,
+  /* Asymmetric 4-bit, eight nibbles per int32 in K order (nibble i of word w
+   * is input 8w+i), fp16 scale and fp16 zero-point per group.
+   * packed [N, K/8] int32, scales [N, K/G] fp16, zeros [N, K/G] fp16.
+   * The reference has no such layout; its definition is this library's.    */
+  B200Q_W4_ASYM_ZP_INT32 = 1
+} b200q_w4_layout;
+
+/* which kernel family a forward call may use */
+typedef enum b200q_kernel {
+  B200Q_KERNEL_AUTO = 0,  /* pick by M                                         */
+  B200Q_KERNEL_SIMT = 1,  /* CUDA-core split-K GEMV (decode rows)              */
+  B200Q_KERNEL_TC = 2     /* tcgen05 tensor-core GEMM, weights on the M side   */
+} b200q_kernel;
+
+/* W8 quantizer flavours */
+typedef enum b200q_w8_mode {
+  /* engine/kernels/w8a16_linear.py:43-47: scale = fp16(max|w|.clamp_min(1e-8)/127),
+   * q = round(w / float(scale_fp16)); scales written as fp16.                */
+  B200Q_W8_SCALE_F16 = 0,
+  /* engine/quantization/int8.py:19-20: scale = max|w|.clamp_min(FLT_EPSILON)/127
+   * kept fp32, q = round(w / scale); scales written as fp32.                 */
+  B200Q_W8_SCALE_F32 = 1
+} b200q_w8_mode;
+
+/* Library identification and diagnostics (host-only, no reference counterpart). */
+int b200q_version(void);
+const char* b200q_status_string(int status);
+/* Kernels this library has launched since load (all devices, all streams). */
+uint64_t b200q_launch_count(void);
+/* Last CUDA error text seen by a failing call on this thread ("" if none). */
+const char* b200q_last_error(void);
+
+/*
+ * Quantize [N,K] weights per output channel to int8 + one scale per row.
+ * Replaces quantize_weight_per_channel (engine/kernels/w8a16_linear.py:43-47)
+ * and the constructor arithmetic of Int8Linear (engine/quantization/int8.py:16-21).
+ *   w        [N, ldw] of w_dtype (f16/bf16/f32), row-major
+ *   q        [N, K] int8, contiguous
+ *   scales   [N] fp16 (mode SCALE_F16) or fp32 (mode SCALE_F32)
+ * A row whose scale rounds to zero (all-zero row in SCALE_F16 mode) gets q = 0.
+ */
+int b200q_quantize_w8_per_channel(const void* w, int w_dtype, int64_t ldw,
+                                  int N, int K, int mode,
+                                  int8_t* q, void* scales, void* stream);
+
+/*
+ * Quantize [N,K] weights to 4 bits in groups of `group` along K and pack.
+ * REF layout replaces quantize_weight_w4_grouped
+ * (engine/kernels/w4a16_format.py:32-50) bit for bit; `zeros` must be NULL.
+ * ASYM layout: per group lo=min(min w,0), hi=max(max w,0),
+ * s=max((hi-lo)/15,1e-8), zp=clamp(rint(-lo/s),0,15), q=clamp(rint(w/s)+zp,0,15),
+ * scale=fp16(s), zero=fp16(zp).
+ * Requires group even and K % group == 0 (ASYM: group % 8 == 0).
+ */
+int b200q_quantize_w4_grouped(const void* w, int w_dtype, int64_t ldw,
+                              int N, int K, int group, int layout,
+                              void* packed, void* scales, void* zeros,
+                              void* stream);
+
+/*
+ * Dequantize packed 4-bit weights into a caller-owned [N, ldo] fp16 matrix:
+ * out[n,k] = fp16(nibble - zp) * fp16(scale), the product taken in fp16
+ * (one rounding).  Replaces w4_dequantize_into
+ * (engine/kernels/w4a16_linear.py:245-274) and is bit-identical to
+ * unpack_w4_reference (engine/kernels/w4a16_format.py:53-69) for the REF layout.
+ */
+int b200q_w4_dequant(const void* packed, const void* scales, const void* zeros,
+                     int layout, int N, int K, int group,
+                     void* out, int64_t ldo, void* stream);
+
+/*
+ * Bytes of workspace a forward call of this geometry may use (0 = none).
+ * `format`: 8 for W8A16, 4 for either INT4 layout.  The workspace must be
+ * zero-filled once when it is allocated; every call leaves it zeroed again
+ * where that matters, so graph replays need no memset.
+ */
+size_t b200q_workspace_bytes(int format, int M, int N, int K);
+
+/*
+ * Wait for `stream`, then read the status word a forward call keeps at the
+ * start of its workspace: B200Q_OK, or B200Q_ERR_DEVICE_WAIT if a kernel gave
+ * up on one of its bounded waits (its output is then undefined).  This call
+ * synchronises and copies four bytes to the host: for tests and diagnostics,
+ * never inside a graph capture.  No reference counterpart.
+ */
+int b200q_workspace_status(const void* workspace, void* stream);
+
+/*
+ * y[M,N] = x[M,K] . (q[N,K] * scales[N])^T (+ bias), fp32 accumulation,
+ * y in the activation dtype.  Replaces w8a16_linear
+ * (engine/kernels/w8a16_linear.py:50-69) and the arithmetic of
+ * Int8Linear.forward (engine/quantization/int8.py:30-33).
+ *   x       [M, ldx]  act_dtype (f16 or bf16)
+ *   qweight [N, ldw]  int8      (ldw % 16 == 0, K % 16 == 0)
+ *   scales  [N]       scale_dtype (f16 or f32)
+ *   bias    [N]       act_dtype, or NULL
+ *   y       [M, ldy]  act_dtype
+ *   workspace/workspace_bytes: see b200q_workspace_bytes; may be NULL when 0.
+ */
+int b200q_w8a16_forward(const void* x, int64_t ldx, int act_dtype,
+                        const int8_t* qweight, int64_t ldw,
+                        const void* scales, int scale_dtype,
+                        const void* bias,
+                        void* y, int64_t ldy,
+                        int M, int N, int K,
+                        void* workspace, size_t workspace_bytes,
+                        int kernel, void* stream);
+
+/*
+ * y[M,N] = x[M,K] . dequant(packed, scales, zeros)^T (+ bias), fp32
+ * accumulation.  Replaces w4a16_linear / w4a16_gemv
+ * (engine/kernels/w4a16_linear.py:77-117, 180-209) and the CUDA branches of
+ * W4A16Linear.forward (engine/quantization/w4a16.py:132-178).
+ *   packed  REF: [N, ldw] uint8 with ldw >= K/2 bytes;
+ *           ASYM: [N, ldw/4] int32 — ldw is always in BYTES (ldw % 16 == 0)
+ *   scales  [N, K/group] fp16 contiguous; zeros likewise (ASYM) or NULL (REF)
+ *   group   multiple of 32 dividing K
+ */
+int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype,
+                        const void* packed, int64_t ldw, int layout,
+                        const void* scales, const void* zeros, int group,
+                        const void* bias,
+                        void* y, int64_t ldy,
+                        int M, int N, int K,
+                        void* workspace, size_t workspace_bytes,
+                        int kernel, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,159 @@
+"""CPU oracle for the weight-only quantized linear path.  TEST INFRASTRUCTURE ONLY.
+
+A numpy restatement of the reference's algorithm (Vaibhav7711/full-inference-engine,
+paths below relative to its root).  Only ``tests/``, ``__graft_entry__.smoke()`` and
+``bench.py``'s CPU-baseline legs may import this module; the product package never does,
+and it fails loudly when its CUDA library is missing rather than coming here.
+
+Parity pin: every function that restates reference code is checked in
+``tests/test_oracle_golden.py`` against (a) the known-answer bytes of the reference's own
+tests (``tests/kernels/test_w4a16_linear.py:18-70``) and (b) golden vectors produced by
+importing the reference itself (``tests/golden/make_golden.py`` holds the generator,
+``tests/golden/*.npz`` its output).
+
+The asymmetric 4-bit layout (``*_asym`` functions) has no counterpart in the reference:
+**parity unpinned** for it.  Its definition is frozen here and in ``include/b200q.h``.
+
+All arithmetic is IEEE: fp32 division (numpy ``/`` on float32), round-half-to-even
+(``np.rint``), fp16 conversion by round-to-nearest-even (``astype(np.float16)``).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+GROUP_SIZE = 128      # engine/kernels/w4a16_format.py:24
+GEMV_MAX_ROWS = 3     # engine/kernels/w4a16_format.py:27
+Q_MAX = 7.0           # engine/kernels/w4a16_format.py:28
+OFFSET = 8            # engine/kernels/w4a16_format.py:29
+
+
+def _nan_to_zero_int(values: np.ndarray, dtype) -> np.ndarray:
+    """torch's CPU float->int conversion sends NaN to 0 (an all-zero W8 row is 0/0)."""
+    cleaned = np.where(np.isnan(values), np.float32(0.0), values)
+    return cleaned.astype(dtype)
+
+
+# --------------------------------------------------------------------------- W8
+def quantize_w8_per_channel(weight: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """engine/kernels/w8a16_linear.py:43-47 — int8 weights + fp16 scale per output row.
+
+    The division that quantises uses the fp16-ROUNDED scale promoted back to fp32.
+    """
+    w = weight.astype(np.float32)
+    s32 = np.maximum(np.abs(w).max(axis=1), np.float32(1e-8)) / np.float32(127.0)
+    s16 = s32.astype(np.float16)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.rint(w / s16.astype(np.float32)[:, None])
+    q = np.clip(q, -127.0, 127.0)          # clip keeps NaN
+    return _nan_to_zero_int(q, np.int8), s16
+
+
+def quantize_w8_int8linear(weight: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """engine/quantization/int8.py:19-20 — Int8Linear's constructor: fp32 scales."""
+    w = weight.astype(np.float32)
+    s32 = np.maximum(np.abs(w).max(axis=1), np.finfo(np.float32).eps) / np.float32(127.0)
+    q = np.clip(np.rint(w / s32[:, None]), -127.0, 127.0)
+    return _nan_to_zero_int(q, np.int8), s32.astype(np.float32)
+
+
+def dequant_w8(q: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """fp32 dequantised weight used by the ground truth: q * scale."""
+    return q.astype(np.float32) * scales.astype(np.float32)[:, None]
+
+
+# --------------------------------------------------------------------------- W4 (reference layout)
+def quantize_w4_grouped(weight: np.ndarray, group_size: int = GROUP_SIZE):
+    """engine/kernels/w4a16_format.py:32-50 — symmetric [-7,7]+8, split-half packing."""
+    if weight.ndim != 2:
+        raise ValueError("weight must be [out_features, in_features]")
+    n, k = weight.shape
+    if group_size % 2 or k % group_size:
+        raise ValueError(f"in_features {k} must be a multiple of an even group_size ({group_size})")
+    groups, half = k // group_size, group_size // 2
+    values = weight.astype(np.float32).reshape(n, groups, group_size)
+    scales = np.maximum(np.abs(values).max(axis=-1), np.float32(1e-8)) / np.float32(Q_MAX)
+    q = np.clip(np.rint(values / scales[..., None]), -Q_MAX, Q_MAX) + OFFSET
+    q = q.astype(np.uint8)
+    low, high = q[..., :half], q[..., half:]
+    packed = (low | (high << 4)).reshape(n, groups * half)
+    return np.ascontiguousarray(packed), np.ascontiguousarray(scales.astype(np.float16))
+
+
+def unpack_w4(packed: np.ndarray, scales: np.ndarray, in_features: int,
+              group_size: int = GROUP_SIZE) -> np.ndarray:
+    """engine/kernels/w4a16_format.py:53-69 — fp16 [N,K]; the product is taken in fp16."""
+    if packed.dtype != np.uint8:
+        raise ValueError("packed weights must be uint8")
+    n = packed.shape[0]
+    groups, half = in_features // group_size, group_size // 2
+    b = packed.reshape(n, groups, half)
+    low = (b & 0x0F).astype(np.int8) - OFFSET
+    high = (b >> 4).astype(np.int8) - OFFSET
+    q = np.concatenate((low, high), axis=-1).astype(np.float16)
+    # numpy multiplies float16 by converting to float32 and rounding the exact product
+    # once, which is an fp16 multiply
+    return (q * scales.astype(np.float16)[..., None]).reshape(n, in_features)
+
+
+def weight_bytes(in_features: int, out_features: int, group_size: int = GROUP_SIZE) -> dict:
+    """engine/kernels/w4a16_format.py:72-77."""
+    return {
+        "fp16": 2 * in_features * out_features,
+        "w8a16": in_features * out_features + 2 * out_features,
+        "w4a16": in_features * out_features // 2 + 2 * out_features * (in_features // group_size),
+    }
+
+
+# --------------------------------------------------------------------------- W4 asymmetric (no reference)
+def quantize_w4_asym(weight: np.ndarray, group_size: int = GROUP_SIZE):
+    """Asymmetric 4-bit, fp16 scale + fp16 zero-point per group, 8 nibbles per int32.
+
+    PARITY UNPINNED: the reference defines no such layout.  Per (row, group):
+    lo=min(min w,0), hi=max(max w,0), s=max((hi-lo)/15,1e-8), zp=clip(rint(-lo/s),0,15),
+    q=clip(rint(w/s)+zp,0,15); word[n,k//8] = sum_i q[n,8*(k//8)+i] << 4i.
+    """
+    if weight.ndim != 2:
+        raise ValueError("weight must be [out_features, in_features]")
+    n, k = weight.shape
+    if group_size % 8 or k % group_size:
+        raise ValueError("in_features must be a multiple of a group_size divisible by 8")
+    groups = k // group_size
+    v = weight.astype(np.float32).reshape(n, groups, group_size)
+    lo = np.minimum(v.min(axis=-1), np.float32(0.0))
+    hi = np.maximum(v.max(axis=-1), np.float32(0.0))
+    s = np.maximum((hi - lo) / np.float32(15.0), np.float32(1e-8)).astype(np.float32)
+    zp = np.clip(np.rint(-lo / s), 0.0, 15.0).astype(np.float32)
+    q = np.clip(np.rint(v / s[..., None]) + zp[..., None], 0.0, 15.0).astype(np.uint32)
+    q = q.reshape(n, k // 8, 8)
+    shifts = (4 * np.arange(8, dtype=np.uint32))[None, None, :]
+    words = np.bitwise_or.reduce(q << shifts, axis=-1).astype(np.uint32)
+    return (np.ascontiguousarray(words.view(np.int32)), s.astype(np.float16), zp.astype(np.float16))
+
+
+def unpack_w4_asym(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, in_features: int,
+                   group_size: int = GROUP_SIZE) -> np.ndarray:
+    """fp16 [N,K]: fp16(nibble - zero) * fp16(scale), product in fp16."""
+    n = packed.shape[0]
+    words = packed.view(np.uint32).reshape(n, in_features // 8, 1)
+    shifts = (4 * np.arange(8, dtype=np.uint32))[None, None, :]
+    q = ((words >> shifts) & 0xF).reshape(n, in_features // group_size, group_size)
+    centred = (q.astype(np.float32) - zeros.astype(np.float32)[..., None]).astype(np.float16)
+    return (centred * scales.astype(np.float16)[..., None]).reshape(n, in_features)
+
+
+# --------------------------------------------------------------------------- ground truth
+def linear_fp32(x: np.ndarray, w_deq: np.ndarray, bias: np.ndarray | None = None) -> np.ndarray:
+    """fp32-accumulated ground truth: x.float() @ W.float().T (+ bias)."""
+    y = x.astype(np.float32) @ w_deq.astype(np.float32).T
+    if bias is not None:
+        y = y + bias.astype(np.float32)[None, :]
+    return y
+
+
+def within_tolerance(actual: np.ndarray, truth: np.ndarray, rel: float = 1e-2) -> tuple[bool, float]:
+    """The acceptance bar: max|actual - truth| <= rel * max|truth|.  Returns (ok, ratio)."""
+    denom = float(np.abs(truth).max())
+    err = float(np.abs(actual.astype(np.float32) - truth).max())
+    ratio = err / denom if denom > 0 else err
+    return ratio <= rel, ratio
