@@ -1,0 +1,565 @@
+"""Benchmark of the weight-only quantized linear forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload c2|c5|c4|c1] [--layout asym|ref]
+
+A *step* is one pass of the hot path over every case of the workload (one forward per
+(shape, M) pair) on synthetic seeded tensors.  The default workload ``c2`` is the INT4
+group-128 M-sweep at the Qwen3-8B MLP shapes; ``c5`` the M=4096 prefill GEMM; ``c4`` the
+W8A16 bf16 sweep; ``c1`` the single W8A16 case the reference runs on CPU.
+
+``value`` is algorithmic GB/s over the whole step with inputs resident in HBM (CUDA-graph
+replay, two weight sets alternated so every weight byte comes from HBM, not L2).  ``e2e`` is
+the same metric through the Python module API with activations in pinned host memory:
+host->device copy, forward, device->host copy of the result, every step.  ``per_case``
+lists every (shape, M) with its own latency, GB/s, TFLOP/s and fraction of roofline, and
+``roofline`` repeats the entry of the kernel that takes the largest share of the step.
+``cpu_baseline`` times the reference's CPU path (dequantise to the activation dtype +
+``F.linear``) on the host cores in the same run.
+
+With ``--impl reference`` only that CPU path runs (rank 0 only under torchrun).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "W8A16/INT4 GEMM TFLOP/s and HBM GB/s vs M (1-4096), Qwen3-8B shapes"
+L2_BYTES = 126 << 20
+
+# Qwen3-8B projections: name -> (K, N)
+SHAPES_8B = {"q": (4096, 4096), "kv": (4096, 2048), "o": (4096, 4096),
+             "gate_up": (4096, 12288), "down": (12288, 4096)}
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; keyed like Case.key.  None = not captured.
+NCU_TRAFFIC_BYTES: dict[str, float] = {}
+
+
+class Case:
+    def __init__(self, name, fmt, m, k, n, dtype, outliers=False):
+        self.name, self.fmt, self.m, self.k, self.n = name, fmt, m, k, n
+        self.dtype, self.outliers = dtype, outliers
+
+    @property
+    def key(self):
+        return f"{self.fmt}:{self.name}:M{self.m}"
+
+    @property
+    def flops(self):
+        return 2.0 * self.m * self.n * self.k
+
+    def weight_bytes(self):
+        groups = self.k // 128
+        if self.fmt == "w8":
+            return self.n * self.k + 2 * self.n
+        if self.fmt == "w4_ref":
+            return self.n * self.k // 2 + 2 * self.n * groups
+        return self.n * self.k // 2 + 4 * self.n * groups
+
+    @property
+    def bytes(self):
+        """Algorithmic bytes: every weight byte once, activations in, outputs out."""
+        return float(self.weight_bytes() + 2 * self.m * self.k + 2 * self.m * self.n)
+
+
+def build_cases(workload: str, layout: str) -> list[Case]:
+    w4 = "w4_asym" if layout == "asym" else "w4_ref"
+    if workload == "c2":
+        return [Case(name, w4, m, *SHAPES_8B[name], torch.float16)
+                for name in ("gate_up", "down") for m in (1, 4, 16, 64, 256)]
+    if workload == "c5":
+        return [Case(name, w4, 4096, *SHAPES_8B[name], torch.bfloat16, outliers=True)
+                for name in ("gate_up", "down")]
+    if workload == "c4":
+        return [Case(name, "w8", m, *SHAPES_8B[name], torch.bfloat16)
+                for name in ("q", "kv", "o", "gate_up", "down") for m in (1, 16, 64, 512)]
+    if workload == "c1":
+        return [Case("gate_0p6b", "w8", 8, 1024, 3072, torch.float16)]
+    raise SystemExit(f"unknown workload {workload}")
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            data = json.load(fh)
+        return {"hbm_gbs": float(data["hbm_gbs"]), "tflops": float(data["bf16_tflops"]),
+                "tflops_sustained": float(data.get("bf16_tflops_sustained", data["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def roofline_entry(case: Case, seconds: float, pk: dict) -> dict:
+    t_hbm = case.bytes / (pk["hbm_gbs"] * 1e9)
+    t_tc = case.flops / (pk["tflops"] * 1e12)
+    if t_hbm >= t_tc:
+        achieved, peak, unit, bound = case.bytes / seconds / 1e9, pk["hbm_gbs"], "GB/s", "hbm"
+    else:
+        achieved, peak, unit, bound = case.flops / seconds / 1e12, pk["tflops"], "TFLOP/s", "tensor"
+    return {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": unit,
+            "frac": round(achieved / peak, 4), "peak_source": pk["source"],
+            "traffic": NCU_TRAFFIC_BYTES.get(case.key)}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the GPU is under load."""
+
+    def __init__(self, index: int, period: float = 0.005):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_flag = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_flag.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self) -> dict:
+        self._stop_flag.set()
+        if self.is_alive():
+            self.join(timeout=1.0)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- inputs
+def make_activation(case: Case, seed: int, device) -> torch.Tensor:
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn(case.m, case.k, generator=gen)
+    if case.outliers:      # 1% of rows scaled x20
+        rows = torch.randperm(case.m, generator=gen)[: max(1, -(-case.m // 100))]
+        x[rows] *= 20.0
+    return x.to(case.dtype).to(device)
+
+
+def make_weight_sets(cases: list[Case], copies: int, device, rank: int = 0, world: int = 1):
+    """Quantized weights per (fmt, shape): `copies` distinct buffers each (L2 rotation).
+
+    With world > 1 each rank keeps rows [rank*N/world, (rank+1)*N/world) of every matrix.
+    """
+    from full_inference_engine_b200.kernels import w4a16_format as w4
+    from full_inference_engine_b200.kernels import w8a16_linear
+
+    sets: dict[tuple, list] = {}
+    for case in cases:
+        key = (case.fmt, case.name)
+        if key in sets:
+            continue
+        gen = torch.Generator(device=device).manual_seed(1000 + len(sets))
+        weight = torch.randn(case.n, case.k, generator=gen, device=device) * 0.02
+        rows = case.n // world
+        weight = weight[rank * rows:(rank + 1) * rows]
+        if case.fmt == "w8":
+            first = w8a16_linear.quantize_weight_per_channel(weight)
+        elif case.fmt == "w4_ref":
+            first = w4.quantize_weight_w4_grouped(weight)
+        else:
+            first = w4.quantize_weight_w4_asym(weight)
+        del weight
+        sets[key] = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
+    return sets
+
+
+def forward(case: Case, x: torch.Tensor, weights: tuple) -> torch.Tensor:
+    from full_inference_engine_b200.kernels import w4a16_linear, w8a16_linear
+
+    if case.fmt == "w8":
+        return w8a16_linear.w8a16_linear(x, weights[0], weights[1])
+    if case.fmt == "w4_ref":
+        return w4a16_linear.w4a16_linear(x, weights[0], weights[1])
+    return w4a16_linear.w4a16_linear(x, weights[0], weights[1], zeros=weights[2])
+
+
+# --------------------------------------------------------------------------- CPU path
+def cpu_inputs(cases: list[Case]):
+    """Host tensors for the reference's CPU path (quantized with the CPU oracle)."""
+    import numpy as np
+
+    from oracle import wq_oracle as oracle
+
+    weights, acts = {}, {}
+    for i, case in enumerate(cases):
+        key = (case.fmt, case.name)
+        if key not in weights:
+            gen = torch.Generator().manual_seed(1000 + len(weights))
+            w = (torch.randn(case.n, case.k, generator=gen) * 0.02).numpy()
+            if case.fmt == "w8":
+                q, s = oracle.quantize_w8_per_channel(w)
+                weights[key] = (torch.from_numpy(q), torch.from_numpy(s))
+            else:     # the only INT4 layout the reference implements
+                p, s = oracle.quantize_w4_grouped(w)
+                weights[key] = (torch.from_numpy(np.ascontiguousarray(p)), torch.from_numpy(s))
+        acts[i] = make_activation(case, 5000 + i, "cpu")
+    return weights, acts
+
+
+def cpu_step(cases, weights, acts, limit=None):
+    from oracle import cpu_path
+
+    done = 0
+    for i, case in enumerate(cases):
+        if limit is not None and i not in limit:
+            continue
+        w = weights[(case.fmt, case.name)]
+        if case.fmt == "w8":
+            cpu_path.int8linear_forward(acts[i], w[0], w[1])
+        else:
+            cpu_path.w4a16_dense_forward(acts[i], w[0], w[1])
+        done += 1
+    return done
+
+
+def time_cpu(cases, budget_s: float = 20.0, min_steps: int = 2):
+    """(seconds per step, steps timed, cores, sample description) on a bounded sample."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    # keep the sample bounded: the M=4096 cases are sampled as they are, but only one pass
+    weights, acts = cpu_inputs(cases)
+    t0 = time.perf_counter()
+    cpu_step(cases, weights, acts)                       # warm-up pass
+    warm = time.perf_counter() - t0
+    steps = max(min_steps, min(10, int(budget_s / max(warm, 1e-3))))
+    if warm > budget_s:
+        steps = 1
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_step(cases, weights, acts)
+        times.append(time.perf_counter() - t0)
+    sample = (f"all {len(cases)} cases of the workload, {steps} timed passes after 1 warm-up, "
+              f"torch CPU ops on {cores} threads; INT4 cases use the reference's own "
+              f"split-half layout")
+    return statistics.median(times), steps, cores, sample
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, cases):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    weights, acts = cpu_inputs(cases)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_step(cases, weights, acts)
+    # bounded: never spend more than a few minutes however large --steps is
+    t_budget, times = 150.0, []
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        cpu_step(cases, weights, acts)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - start > t_budget:
+            break
+    sec = sum(times) / len(times)
+    total_bytes = sum(c.bytes for c in cases)
+    total_flops = sum(c.flops for c in cases)
+    value = total_bytes / sec / 1e9
+    sample = (f"{len(times)} of {args.steps} requested passes over all {len(cases)} cases "
+              f"(bounded to {t_budget:.0f} s), torch CPU dequantise + F.linear on {cores} threads; "
+              "the oracle's port of the reference CPU path (the reference tree is not on this box)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "GB/s",
+        "tflops": round(total_flops / sec / 1e12, 5), "n_gpus": args.gpus, "steps": len(times),
+        "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16/bf16 activations, fp32 accumulate",
+        "data": "synthetic", "config": config_dict(args, cases, rotation=None),
+        "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, cases, rotation):
+    return {
+        "workload": {"c2": "config 2: INT4 g128 M-sweep {1,4,16,64,256} at Qwen3-8B gate/up "
+                           "(4096->12288) and down (12288->4096), fp16 activations",
+                     "c5": "config 5: INT4 g128 prefill M=4096 bf16 with 1% outlier rows, "
+                           "gate/up and down",
+                     "c4": "config 4: W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, M in {1,16,64,512}",
+                     "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16"}[args.workload],
+        "layout": {"asym": "asymmetric int32 x8 nibbles + fp16 scale and zero-point",
+                   "ref": "reference split-half uint8 + fp16 scale"}[args.layout]
+        if cases[0].fmt != "w8" else "int8 per-channel fp16 scale",
+        "cases": len(cases),
+        "parallelism": f"N-sharded x{args.gpus} + all-gather" if args.gpus > 1 else "single GPU",
+        "l2": rotation,
+    }
+
+
+# --------------------------------------------------------------------------- B200 arm
+def run_b200(args, cases):
+    import torch.distributed as dist
+
+    from full_inference_engine_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    pk = peaks()
+    copies = 10 if args.workload in ("c2", "c1") else (4 if args.workload == "c4" else 3)
+    weight_sets = make_weight_sets(cases, copies, device, rank, world)
+    acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
+    # per-rank view of each case
+    local_cases = [Case(c.name, c.fmt, c.m, c.k, c.n // world, c.dtype, c.outliers) for c in cases]
+    gathered = [torch.empty(world, c.m, c.n // world, dtype=c.dtype, device=device) if world > 1 else None
+                for c in cases]
+
+    def one_step(variant: int):
+        outs = []
+        for i, case in enumerate(local_cases):
+            sets = weight_sets[(case.fmt, case.name)]
+            w = sets[(i + variant * len(local_cases)) % len(sets)]
+            y = forward(case, acts[i], w)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[i], y)
+            outs.append(y)
+        return outs
+
+    step_weight_bytes = sum(c.weight_bytes() for c in local_cases)
+    rotation = (f"inputs larger than L2: each case reads its own weight buffer and two step "
+                f"variants alternate, {2 * step_weight_bytes / 2**20:.0f} MiB of distinct weights "
+                f"between reuses (L2 = 126 MiB)")
+
+    # eager warm-up (also sizes the workspace), then capture two step variants
+    for v in (0, 1):
+        one_step(v)
+    torch.cuda.synchronize()
+    launches_before = _lib.launch_count()
+    graphs = []
+    use_graph = True
+    try:
+        for v in (0, 1):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                one_step(v)
+            graphs.append(g)
+    except Exception as exc:      # NCCL capture unsupported etc.: time eager launches instead
+        use_graph = False
+        graphs = []
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(f"# graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+    launches_per_step = (_lib.launch_count() - launches_before) // 2 if use_graph else len(cases)
+
+    def run_step(i):
+        if use_graph:
+            graphs[i & 1].replay()
+        else:
+            one_step(i & 1)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    # bring the clocks up, then the requested warm-up steps
+    t_end = time.perf_counter() + 0.3
+    i = 0
+    while time.perf_counter() < t_end:
+        run_step(i)
+        i += 1
+        if i % 64 == 0:
+            torch.cuda.synchronize()
+    for j in range(max(3, args.warmup)):
+        run_step(j)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for j in range(args.steps):
+        run_step(j)
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms_total = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms_total], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # ---- per-case latency (roofline): R back-to-back launches over rotating weight copies
+    per_case = []
+    for i, case in enumerate(local_cases):
+        sets = weight_sets[(case.fmt, case.name)]
+        reps = len(sets)
+        for w in sets[:2]:
+            forward(case, acts[i], w)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for w in sets:
+                forward(case, acts[i], w)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) / reps)
+        sec = statistics.median(times) * 1e-3
+        entry = {"case": case.key, "M": case.m, "K": case.k, "N": case.n, "us": round(sec * 1e6, 2),
+                 "GBps": round(case.bytes / sec / 1e9, 1), "TFLOPs": round(case.flops / sec / 1e12, 2)}
+        entry.update(roofline_entry(case, sec, pk))
+        entry["frac_of_nominal"] = round(
+            max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
+        per_case.append(entry)
+        del g
+    clocks = sampler.stop()
+
+    # ---- end to end: pinned host activations in, host results out, through the public API
+    host_x = [torch.empty(c.m, c.k, dtype=c.dtype).pin_memory().copy_(acts[i].cpu()) for i, c in enumerate(cases)]
+    host_y = [torch.empty(c.m, c.n // world, dtype=c.dtype).pin_memory() for c in cases]
+    dev_x = [torch.empty_like(a) for a in acts]
+
+    def e2e_step(variant):
+        for i, case in enumerate(local_cases):
+            dev_x[i].copy_(host_x[i], non_blocking=True)
+            sets = weight_sets[(case.fmt, case.name)]
+            y = forward(case, dev_x[i], sets[(i + variant * len(local_cases)) % len(sets)])
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[i], y)
+            host_y[i].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()          # the step's results are on the host
+        return float(host_y[-1][0, 0])
+
+    for j in range(3):
+        e2e_step(j & 1)
+    if world > 1:
+        dist.barrier()
+    e2e_steps = max(3, min(args.steps, 50))
+    t0 = time.perf_counter()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for j in range(e2e_steps):
+        e2e_step(j & 1)
+    e.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    status = _lib.library().b200q_workspace_status(_lib.workspace_for(device, 256).data_ptr(), None)
+
+    if rank == 0:
+        total_bytes = sum(c.bytes for c in cases)          # whole job, all ranks
+        total_flops = sum(c.flops for c in cases)
+        dominant = max(per_case, key=lambda r: r["us"])
+        step_us = sum(r["us"] for r in per_case)
+        line = {
+            "metric": METRIC, "value": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "unit": "GB/s",
+            "tflops": round(total_flops / (ms_step * 1e-3) / 1e12, 3),
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16/bf16 activations, fp32 accumulate", "data": "synthetic",
+            "config": config_dict(args, cases, rotation),
+            "roofline": {k: dominant[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
+            | {"kernel": dominant["case"], "share_of_step": round(dominant["us"] / step_us, 3),
+               "peak_source": pk["source"]},
+            "per_case": per_case,
+            "clocks": clocks,
+            "e2e": {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                    "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": int(sum(2 * c.m * c.k for c in cases)),
+                    "d2h_bytes_per_step": int(sum(2 * c.m * (c.n // world) for c in cases)),
+                    "note": "weights stay resident on the device (module state); activations come "
+                            "from pinned host memory and results return to it every step"},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "timing": "cuda-graph replay" if use_graph else "eager launches",
+            "device_status": status,
+        }
+        if world == 1:
+            sec, steps, cores, sample = time_cpu(cases)
+            line["cpu_baseline"] = {"value": round(total_bytes / sec / 1e9, 4), "unit": "GB/s",
+                                    "cores": cores, "kind": "port", "sample": sample,
+                                    "ms_per_step": round(sec * 1e3, 2)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c4", "c5"])
+    ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
+    args = ap.parse_args()
+    cases = build_cases(args.workload, args.layout)
+    if args.impl == "reference":
+        run_reference(args, cases)
+    else:
+        run_b200(args, cases)
+
+
+if __name__ == "__main__":
+    main()

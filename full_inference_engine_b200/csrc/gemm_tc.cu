@@ -502,6 +502,12 @@ static bool get_tensor_map(CUtensorMap* out, const void* ptr, CUtensorMapDataTyp
   return true;
 }
 
+// Workspace layout (fixed, so that calls of different geometry never see one another's
+// leftovers as counters): [0,256) status word, [256, 64 KiB) split-K tile counters (always
+// zero between launches), then the fp32 partials.
+constexpr size_t kWsHeaderBytes = 64 * 1024;
+constexpr int kMaxSplitTiles = static_cast<int>((kWsHeaderBytes - 256) / sizeof(unsigned));
+
 struct TcPlan {
   int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, tmem_cols;
   size_t smem_bytes;
@@ -561,7 +567,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
     }
     if (eff >= 0.9) break;
   }
-  if (tiles >= slots) best = 1;
+  if (tiles >= slots || tiles > kMaxSplitTiles) best = 1;
   pl.kb_per_split = (pl.kb_total + best - 1) / best;
   pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
   return pl;
@@ -570,9 +576,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
 size_t tc_workspace_bytes(int format, int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   TcPlan pl = make_plan(format, M, N, K);
-  // status word + counters always; partials only when split
-  size_t bytes = 256 + sizeof(unsigned) * static_cast<size_t>(pl.m_tiles) * pl.n_tiles;
-  bytes = (bytes + 255) / 256 * 256;
+  size_t bytes = kWsHeaderBytes;
   if (pl.splits > 1) bytes += sizeof(float) * static_cast<size_t>(pl.splits) * M * N;
   return bytes;
 }
@@ -639,9 +643,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   p.status = reinterpret_cast<unsigned*>(ws);
   p.counters = reinterpret_cast<unsigned*>(ws + 256);
-  size_t off = 256 + sizeof(unsigned) * static_cast<size_t>(pl.m_tiles) * pl.n_tiles;
-  off = (off + 255) / 256 * 256;
-  p.partial = reinterpret_cast<float*>(ws + off);
+  p.partial = reinterpret_cast<float*>(ws + kWsHeaderBytes);
 
   dim3 grid(pl.n_tiles, pl.m_tiles, pl.splits), block(kTcThreads);
   wq_gemm_tc_kernel<FMT, T><<<grid, block, pl.smem_bytes, a.stream>>>(tm_w, tm_x, p);
