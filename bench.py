@@ -211,10 +211,10 @@ def forward(case: Case, x: torch.Tensor, weights: tuple) -> torch.Tensor:
     from full_inference_engine_b200.kernels import w4a16_linear, w8a16_linear
 
     if case.fmt == "w8":
-        return w8a16_linear.w8a16_linear(x, weights[0], weights[1])
+        return w8a16_linear.w8a16_linear(x, weights[0], weights[1], static_weights=True)
     if case.fmt == "w4_ref":
-        return w4a16_linear.w4a16_linear(x, weights[0], weights[1])
-    return w4a16_linear.w4a16_linear(x, weights[0], weights[1], zeros=weights[2])
+        return w4a16_linear.w4a16_linear(x, weights[0], weights[1], static_weights=True)
+    return w4a16_linear.w4a16_linear(x, weights[0], weights[1], zeros=weights[2], static_weights=True)
 
 
 # --------------------------------------------------------------------------- CPU path
@@ -545,6 +545,22 @@ def run_b200(args, cases):
         dist.destroy_process_group()
 
 
+def run_profile(args, cases):
+    """Plain eager launches, one weight buffer per launch: the command ncu wraps."""
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    weight_sets = make_weight_sets(cases, 6, device)
+    acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
+    n = 0
+    for step in range(max(1, args.warmup) + args.steps):
+        for i, case in enumerate(cases):
+            sets = weight_sets[(case.fmt, case.name)]
+            forward(case, acts[i], sets[(step + i) % len(sets)])
+            n += 1
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_launches": n, "cases": [c.key for c in cases]}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -553,8 +569,19 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c4", "c5"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
+    ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
+    ap.add_argument("--profile", action="store_true",
+                    help="eager launches of the selected cases only (for ncu): no graphs, no e2e, no CPU leg")
     args = ap.parse_args()
     cases = build_cases(args.workload, args.layout)
+    if args.cases:
+        wanted = [w for w in args.cases.split(",") if w]
+        cases = [c for c in cases if any(c.key.endswith(w) or w in c.key for w in wanted)]
+        if not cases:
+            raise SystemExit("--cases matched nothing")
+    if args.profile:
+        run_profile(args, cases)
+        return
     if args.impl == "reference":
         run_reference(args, cases)
     else:

@@ -32,7 +32,9 @@ int note_launch() {
 // stream.  Everything wider is a contraction and belongs on the tensor cores.
 constexpr int kSimtMaxRows = 2;
 
-static int run_forward(const ForwardArgs& a, int kernel) {
+static int run_forward(ForwardArgs& a, int kernel_and_flags) {
+  a.static_weights = (kernel_and_flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
+  const int kernel = kernel_and_flags & 0xFF;
   if (kernel == B200Q_KERNEL_SIMT) return launch_forward_simt(a);
   if (kernel == B200Q_KERNEL_TC) return launch_forward_tc(a);
   if (kernel != B200Q_KERNEL_AUTO) return B200Q_ERR_INVALID;

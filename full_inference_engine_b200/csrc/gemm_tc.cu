@@ -58,6 +58,7 @@ struct TcParams {
   int splits;
   int np, na, nx;    // ring depths
   float* partial;    // [splits, M, N] fp32 (split-K only)
+  int static_weights;  // weights/scales/bias may be read ahead of the stream order
   unsigned* counters;  // [m_tiles * n_tiles], zero between launches
   unsigned* status;    // device status word (non-zero: a bounded wait expired)
 };
@@ -123,17 +124,73 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
 }
 
+#ifdef B200Q_TRACE
+// Debug builds only: per-block cycle stamps of the pipeline phases.
+__device__ unsigned long long g_trace[1024 * 64];
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define B200Q_STAMP(slot)                                                              \
+  do {                                                                                 \
+    if (trace_cta < 1024 && (slot) < 64) g_trace[trace_cta * 64 + (slot)] = clock64(); \
+  } while (0)
+#define B200Q_STAMP_NS(slot)                                                             \
+  do {                                                                                   \
+    if (trace_cta < 1024 && (slot) < 64) g_trace[trace_cta * 64 + (slot)] = global_ns(); \
+  } while (0)
+#else
+#define B200Q_STAMP(slot)
+#define B200Q_STAMP_NS(slot)
+#endif
+
+// Per-(row, group) parameters of the 4-bit formats, fetched eight groups at a time
+// (one 16-byte load per row) one chunk ahead of use, so that their latency never sits
+// between two pipeline stages.  When K/128 is not a multiple of 8 a chunk is one group.
+struct GroupChunk {
+  uint4 s[2];   // scales of the thread's two rows
+  uint4 z[2];   // zero-points (asymmetric layout only)
+};
+
+__device__ __forceinline__ __half pick_half(const uint4& v, int idx) {
+  const uint32_t w = (idx & 4) ? ((idx & 2) ? v.w : v.z) : ((idx & 2) ? v.y : v.x);
+  return __ushort_as_half(static_cast<unsigned short>((idx & 1) ? (w >> 16) : (w & 0xFFFFu)));
+}
+
+template <int FMT>
+__device__ __forceinline__ void load_group_chunk(GroupChunk& g, const TcParams& p, int chunk,
+                                                 bool vec, int n0, int n1) {
+  const int rows[2] = {n0, n1};
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    g.s[j] = make_uint4(0u, 0u, 0u, 0u);
+    g.z[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (rows[j] < p.N) {
+      const int64_t base = static_cast<int64_t>(rows[j]) * p.groups;
+      const __half* sp = reinterpret_cast<const __half*>(p.scales) + base;
+      if (vec) {
+        g.s[j] = __ldg(reinterpret_cast<const uint4*>(sp + chunk * 8));
+        if (FMT == FMT_W4_ASYM) g.z[j] = __ldg(reinterpret_cast<const uint4*>(p.zeros + base + chunk * 8));
+      } else {
+        g.s[j].x = __half_as_ushort(__ldg(sp + chunk));
+        if (FMT == FMT_W4_ASYM) g.z[j].x = __half_as_ushort(__ldg(p.zeros + base + chunk));
+      }
+    }
+  }
+}
+
 template <int FMT, typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
 wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                   const TcParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled operand tiles
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int x_stage_bytes = p.tok * 256;                 // two atoms of [tok x 128 B]
+  const int x_atom_bytes = p.tok * 128;                  // one 64-wide K atom of [tok x 128 B]
   const uint32_t a_ring = smem_base;
   const uint32_t x_ring = a_ring + p.na * kStageBytesA;
-  const uint32_t p_ring = x_ring + p.nx * x_stage_bytes;
+  const uint32_t p_ring = x_ring + p.nx * x_atom_bytes;
   const uint32_t bars = p_ring + p.np * PackedStage<FMT>::kBytes;
   // barrier slots (8 bytes each)
   const uint32_t p_full = bars;
@@ -158,6 +215,13 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
   const int nkb = max(kb1 - kb0, 0);
+#ifdef B200Q_TRACE
+  const int trace_cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (threadIdx.x == 0) {
+    B200Q_STAMP(0);
+    B200Q_STAMP_NS(1);
+  }
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxRing; ++i) {
@@ -183,40 +247,74 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_p;
+  if (threadIdx.x == 0) {
+    B200Q_STAMP(2);
+    // Let the next kernel in the stream begin its own set-up; it orders itself behind
+    // this grid with griddepcontrol.wait before it touches anything this grid writes.
+    grid_launch_dependents();
+  }
+  // With static weights the weight stream may start before the previous kernel in the
+  // stream has finished; activations, outputs and the workspace always wait for it.
+  if (!p.static_weights) grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // One thread feeds two independent rings, polling whichever has a free slot: packed
+    // weights (one stage per K block) and activations (one 64-wide atom per slot).
     if (elect_one()) {
-      int issued = 0;
+      int ip = 0, ix = 0;                       // weight stages / activation atoms issued
+      const int nx_total = 2 * nkb;
+      bool waited = !p.static_weights;
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int kb = kb0 + i;
-        const int sp = i % p.np, sx = i % p.nx;
-        ok = wait_or_abort(p_empty + 8 * sp, ((i / p.np) & 1) ^ 1, abort_p);
-        if (!ok) break;
-        const uint32_t pdst = p_ring + sp * PackedStage<FMT>::kBytes;
-        mbar_arrive_expect_tx(p_full + 8 * sp, PackedStage<FMT>::kBytes);
-        if (FMT == FMT_W8) {
-          tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 128, n_tile * kBlockN);
-          tma_load_2d(pdst + kBlockN * 64, &tm_w, p_full + 8 * sp, kb * 128 + 64, n_tile * kBlockN);
-        } else {
-          tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 64, n_tile * kBlockN);
+      uint32_t idle = 0;
+      while (ip < nkb || ix < nx_total) {
+        bool progress = false;
+        if (ip < nkb) {
+          const int sp = ip % p.np;
+          if (mbar_test_wait(p_empty + 8 * sp, ((ip / p.np) & 1) ^ 1)) {
+            const int kb = kb0 + ip;
+            const uint32_t pdst = p_ring + sp * PackedStage<FMT>::kBytes;
+            mbar_arrive_expect_tx(p_full + 8 * sp, PackedStage<FMT>::kBytes);
+            if (FMT == FMT_W8) {
+              tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 128, n_tile * kBlockN);
+              tma_load_2d(pdst + kBlockN * 64, &tm_w, p_full + 8 * sp, kb * 128 + 64, n_tile * kBlockN);
+            } else {
+              tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 64, n_tile * kBlockN);
+            }
+            if (ip == 0) B200Q_STAMP(3);
+            ++ip;
+            progress = true;
+          }
         }
-        ok = wait_or_abort(x_empty + 8 * sx, ((i / p.nx) & 1) ^ 1, abort_p);
-        if (!ok) break;
-        const uint32_t xdst = x_ring + sx * x_stage_bytes;
-        mbar_arrive_expect_tx(x_full + 8 * sx, static_cast<uint32_t>(x_stage_bytes));
-        tma_load_2d(xdst, &tm_x, x_full + 8 * sx, kb * kBlockK, m_tile * p.tok);
-        tma_load_2d(xdst + p.tok * 128, &tm_x, x_full + 8 * sx, kb * kBlockK + 64, m_tile * p.tok);
-        issued = i + 1;
+        if (!waited && (ip >= nkb || ip >= p.np)) {
+          // the weight ring is as far ahead as it can get: now order behind the stream
+          grid_dependency_wait();
+          waited = true;
+          progress = true;
+        }
+        if (waited && ix < nx_total) {
+          const int sx = ix % p.nx;
+          if (mbar_test_wait(x_empty + 8 * sx, ((ix / p.nx) & 1) ^ 1)) {
+            mbar_arrive_expect_tx(x_full + 8 * sx, static_cast<uint32_t>(x_atom_bytes));
+            tma_load_2d(x_ring + sx * x_atom_bytes, &tm_x, x_full + 8 * sx,
+                        (kb0 + (ix >> 1)) * kBlockK + 64 * (ix & 1), m_tile * p.tok);
+            ++ix;
+            progress = true;
+          }
+        }
+        if (progress) {
+          idle = 0;
+        } else if (++idle > (kMaxPolls << 4) || ((idle & 0x3FF) == 0 && *abort_p)) {
+          ok = false;
+          break;
+        }
       }
+      B200Q_STAMP(4);
       if (!ok) flag_failure(abort_p, p.status, 1u);
       if (*abort_p) {
         // let the copies already in flight land before the block's shared memory is released
-        for (int i = max(0, issued - kMaxRing); i < issued; ++i) {
-          if (i >= issued - p.np) mbar_wait(p_full + 8 * (i % p.np), (i / p.np) & 1);
-          if (i >= issued - p.nx) mbar_wait(x_full + 8 * (i % p.nx), (i / p.nx) & 1);
-        }
+        for (int i = max(0, ip - p.np); i < ip; ++i) mbar_wait(p_full + 8 * (i % p.np), (i / p.np) & 1);
+        for (int i = max(0, ix - p.nx); i < ix; ++i) mbar_wait(x_full + 8 * (i % p.nx), (i / p.nx) & 1);
       }
     }
   } else if (warp == 1) {
@@ -224,26 +322,31 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     if (elect_one()) {
       bool ok = true;
       for (int i = 0; i < nkb && ok; ++i) {
-        const int sa = i % p.na, sx = i % p.nx;
-        ok = wait_or_abort(x_full + 8 * sx, (i / p.nx) & 1, abort_p) &&
-             wait_or_abort(a_full + 8 * sa, (i / p.na) & 1, abort_p);
+        const int sa = i % p.na;
+        ok = wait_or_abort(a_full + 8 * sa, (i / p.na) & 1, abort_p);
         if (!ok) break;
-        tc_fence_after_sync();
+        if (i < 12) B200Q_STAMP(8 + 2 * i);
         const uint32_t a_stage = a_ring + sa * kStageBytesA;
-        const uint32_t x_stage = x_ring + sx * x_stage_bytes;
 #pragma unroll
         for (int atom = 0; atom < 2; ++atom) {
+          const int xi = 2 * i + atom;
+          const int sx = xi % p.nx;
+          ok = wait_or_abort(x_full + 8 * sx, (xi / p.nx) & 1, abort_p);
+          if (!ok) break;
+          tc_fence_after_sync();
           const uint64_t adesc = umma_desc_sw128(a_stage + atom * kAtomBytesA);
-          const uint64_t bdesc = umma_desc_sw128(x_stage + atom * p.tok * 128);
+          const uint64_t bdesc = umma_desc_sw128(x_ring + sx * x_atom_bytes);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // advance 16 elements = 32 bytes along K inside the swizzle atom
             umma_f16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc,
                         (i > 0 || atom > 0 || k > 0) ? 1u : 0u);
           }
+          umma_commit(x_empty + 8 * sx);
         }
-        umma_commit(x_empty + 8 * sx);
+        if (!ok) break;
         umma_commit(a_empty + 8 * sa);
+        if (i < 12) B200Q_STAMP(9 + 2 * i);
       }
       if (!ok) flag_failure(abort_p, p.status, 2u);
       umma_commit(acc_full);
@@ -253,25 +356,34 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int td = threadIdx.x - 64;          // 0..255
     const int q = td & 3;                      // 16-byte vector inside a 64-byte packed row
     const int r_base = td >> 2;                // 0..63
+    const int row_n0 = n_tile * kBlockN + r_base, row_n1 = row_n0 + 64;
+    const bool vec = (p.groups & 7) == 0;
+    const int chunk_shift = vec ? 3 : 0;
+    GroupChunk cur, nxt;
+    int cur_chunk = kb0 >> chunk_shift;
+    const int last_chunk = (kb1 - 1) >> chunk_shift;
+    if (FMT != FMT_W8 && nkb > 0) {
+      load_group_chunk<FMT>(cur, p, cur_chunk, vec, row_n0, row_n1);
+      if (cur_chunk < last_chunk) load_group_chunk<FMT>(nxt, p, cur_chunk + 1, vec, row_n0, row_n1);
+    }
     bool ok = true;
     for (int i = 0; i < nkb && ok; ++i) {
       const int kb = kb0 + i;
       const int sp = i % p.np, sa = i % p.na;
-      // group parameters first: their latency hides behind the barrier waits
       __half2 scale2[2];
       __half2 bias_lo[2], nbias_hi[2];
       if (FMT != FMT_W8) {
+        const int chunk = kb >> chunk_shift;
+        if (chunk != cur_chunk) {
+          cur = nxt;
+          cur_chunk = chunk;
+          if (chunk < last_chunk) load_group_chunk<FMT>(nxt, p, chunk + 1, vec, row_n0, row_n1);
+        }
+        const int idx = vec ? (kb & 7) : 0;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const int n = n_tile * kBlockN + r_base + 64 * j;
-          __half s = __float2half_rn(0.0f);
-          float zp = 8.0f;
-          if (n < p.N) {
-            const int64_t si = static_cast<int64_t>(n) * p.groups + kb;
-            s = __ldg(reinterpret_cast<const __half*>(p.scales) + si);
-            if (FMT == FMT_W4_ASYM) zp = __half2float(__ldg(p.zeros + si));
-          }
-          scale2[j] = __half2half2(s);
+          const float zp = (FMT == FMT_W4_ASYM) ? __half2float(pick_half(cur.z[j], idx)) : 8.0f;
+          scale2[j] = __half2half2(pick_half(cur.s[j], idx));
           bias_lo[j] = __float2half2_rn(1024.0f + zp);
           nbias_hi[j] = __float2half2_rn(-(64.0f + zp));
         }
@@ -279,6 +391,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       ok = wait_or_abort(p_full + 8 * sp, (i / p.np) & 1, abort_p) &&
            wait_or_abort(a_empty + 8 * sa, ((i / p.na) & 1) ^ 1, abort_p);
       if (!ok) break;
+      if (td == 0 && i < 12) B200Q_STAMP(32 + 2 * i);
       const uint32_t p_stage = p_ring + sp * PackedStage<FMT>::kBytes;
       const uint32_t a_stage = a_ring + sa * kStageBytesA;
       if (FMT == FMT_W4_REF) {
@@ -347,6 +460,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         mbar_arrive(a_full + 8 * sa);
         mbar_arrive(p_empty + 8 * sp);
       }
+      if (td == 0 && i < 12) B200Q_STAMP(33 + 2 * i);
     }
     if (!ok) flag_failure(abort_p, p.status, 4u);
 
@@ -354,13 +468,17 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     bool acc_ok = wait_or_abort(acc_full, 0, abort_p);
     if (!acc_ok) flag_failure(abort_p, p.status, 8u);
     tc_fence_after_sync();
+    if (td == 0) B200Q_STAMP(56);
     acc_ok = __all_sync(0xffffffffu, acc_ok && !*abort_p) != 0;
+    grid_dependency_wait();            // outputs and workspace belong to the stream order
     const int lane_quarter = warp & 3;                   // TMEM lanes this warp may read
     const int col_half = (warp - 2) >> 2;                // which half of the token columns
-    const int n = n_tile * kBlockN + lane_quarter * 32 + lane;
+    const int ch = lane_quarter * 32 + lane;             // channel inside the tile
+    const int n = n_tile * kBlockN + ch;
     const int half_cols = p.tok >> 1;
     const int c_begin = col_half * half_cols;
     const int m_base = m_tile * p.tok;
+    const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_quarter * 32) << 16);
     T* yT = static_cast<T*>(p.y);
     float ch_scale = 1.0f, ch_bias = 0.0f;
     if (n < p.N) {
@@ -369,28 +487,69 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                                   : __half2float(reinterpret_cast<const __half*>(p.scales)[n]);
       if (p.bias != nullptr) ch_bias = static_cast<float>(static_cast<const T*>(p.bias)[n]);
     }
-    if (acc_ok && nkb > 0) {
-      for (int c = 0; c < half_cols; c += 8) {
-        uint32_t r[8];
-        tmem_ld_x8(tmem_base + (static_cast<uint32_t>(lane_quarter * 32) << 16) + (c_begin + c), r);
-        tmem_ld_wait();
-        if (n < p.N) {
+    if (p.splits == 1) {
+      // accumulators -> output dtype -> shared memory as [token][128 channels], then
+      // 16-byte row-contiguous stores (the operand rings are idle by now)
+      const uint32_t stage = x_ring;
+      const bool vec_out = (p.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) &&
+                           (p.nx * x_atom_bytes >= p.tok * 256);
+      if (acc_ok && nkb > 0) {
+        for (int c = 0; c < half_cols; c += 8) {
+          uint32_t r[8];
+          tmem_ld_x8(tmem_row + (c_begin + c), r);
+          tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int m = m_base + c_begin + c + j;
-            if (m < p.M) {
-              const float v = __uint_as_float(r[j]);
-              if (p.splits == 1) {
-                yT[static_cast<int64_t>(m) * p.ldy + n] = from_float<T>(v * ch_scale + ch_bias);
-              } else {
-                p.partial[(static_cast<int64_t>(split) * p.M + m) * p.N + n] = v;
-              }
+            const T v = from_float<T>(__uint_as_float(r[j]) * ch_scale + ch_bias);
+            if (vec_out) {
+              const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + ch * 2),
+                           "h"(bits)
+                           : "memory");
+            } else {
+              const int m = m_base + c_begin + c + j;
+              if (n < p.N && m < p.M) yT[static_cast<int64_t>(m) * p.ldy + n] = v;
             }
           }
         }
       }
-    }
-    if (p.splits > 1) {
+      if (vec_out) {
+        asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+        if (acc_ok && nkb > 0) {
+          const int chunk = td & 15;                       // 8 channels = 16 bytes
+          const int n_c = n_tile * kBlockN + chunk * 8;
+          const int rows = min(p.tok, p.M - m_base);
+          for (int r = td >> 4; r < rows; r += kDequantThreads / 16) {
+            const uint4 v = ld_shared_v4(stage + r * 256 + chunk * 16);
+            T* dst = yT + static_cast<int64_t>(m_base + r) * p.ldy + n_c;
+            if (n_c + 8 <= p.N) {
+              *reinterpret_cast<uint4*>(dst) = v;
+            } else {
+              const T* e = reinterpret_cast<const T*>(&v);
+              for (int k = 0; k < 8; ++k)
+                if (n_c + k < p.N) dst[k] = e[k];
+            }
+          }
+        }
+      }
+      if (td == 0) B200Q_STAMP(57);
+    } else {
+      if (acc_ok && nkb > 0) {
+        for (int c = 0; c < half_cols; c += 8) {
+          uint32_t r[8];
+          tmem_ld_x8(tmem_row + (c_begin + c), r);
+          tmem_ld_wait();
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int m = m_base + c_begin + c + j;
+              if (m < p.M)
+                p.partial[(static_cast<int64_t>(split) * p.M + m) * p.N + n] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+      if (td == 0) B200Q_STAMP(57);
       // last block to arrive for this tile sums the partials in split order
       __threadfence();
       asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
@@ -403,13 +562,25 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (*last_p) {
         __threadfence();
         if (n < p.N) {
-          for (int c = 0; c < half_cols; ++c) {
-            const int m = m_base + c_begin + c;
-            if (m >= p.M) break;
-            float v = 0.0f;
-            for (int z = 0; z < p.splits; ++z)
-              v += __ldcg(p.partial + (static_cast<int64_t>(z) * p.M + m) * p.N + n);
-            yT[static_cast<int64_t>(m) * p.ldy + n] = from_float<T>(v * ch_scale + ch_bias);
+          for (int c = 0; c < half_cols; c += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+            for (int z = 0; z < p.splits; ++z) {
+              float t[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int m = min(m_base + c_begin + c + j, p.M - 1);
+                t[j] = __ldcg(p.partial + (static_cast<int64_t>(z) * p.M + m) * p.N + n);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += t[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int m = m_base + c_begin + c + j;
+              if (m < p.M) yT[static_cast<int64_t>(m) * p.ldy + n] = from_float<T>(v[j] * ch_scale + ch_bias);
+            }
           }
         }
         if (td == 0) *counter = 0u;      // ready for the next launch / graph replay
@@ -417,13 +588,24 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   }
 
+  if (threadIdx.x == 64) B200Q_STAMP(58);
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    B200Q_STAMP(59);
+    B200Q_STAMP_NS(60);
+  }
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
   }
 }
+
+#ifdef B200Q_TRACE
+extern "C" int b200q_trace_read(unsigned long long* host, size_t count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, count * sizeof(unsigned long long)));
+}
+#endif
 
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -528,24 +710,37 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   while (cols < tok) cols <<= 1;
   pl.tmem_cols = cols;
 
-  // Ring depths.  Narrow token tiles are the HBM-bound regime: keep a block
-  // under half an SM's shared memory so two blocks are resident and one
-  // block's set-up and epilogue overlap the other's weight stream.
+  // Ring depths.  Narrow token tiles are the HBM-bound regime: keep a block under half an
+  // SM's shared memory so that two blocks are resident and one block's set-up and epilogue
+  // overlap the other's weight stream.  Wide tiles take the whole SM and deeper rings.
   const int pbytes = packed_stage_bytes(format);
-  const int xbytes = tok * 256;
+  const int xbytes = tok * 128;                    // one activation atom
   auto total = [&](int np, int na, int nx) {
     return static_cast<size_t>(na) * kStageBytesA + static_cast<size_t>(nx) * xbytes +
            static_cast<size_t>(np) * pbytes + 1024 /*alignment*/ + 8 * kMaxRing * 6 + 64;
   };
-  const bool two_per_sm = tok <= 32;
-  const size_t budget = two_per_sm ? 112 * 1024 : static_cast<size_t>(kSmemBudget);
+  const size_t half_sm = 115712;                   // (228 KiB - 2 x 1 KiB reserved) / 2
+  const bool two_per_sm = tok <= 32 && total(2, 2, 4) <= half_sm;
   pl.na = 2;
   pl.nx = 2;
   pl.np = 2;
-  while (pl.np < (two_per_sm ? kMaxRing : 6) && total(pl.np + 1, pl.na, pl.nx) <= budget) ++pl.np;
-  if (!two_per_sm) {
-    while (pl.nx < 4 && total(pl.np, pl.na, pl.nx + 1) <= budget) ++pl.nx;
-    while (pl.na < 3 && total(pl.np, pl.na + 1, pl.nx) <= budget) ++pl.na;
+  if (two_per_sm) {
+    pl.nx = 4;
+    while (pl.np < kMaxRing && total(pl.np + 1, pl.na, pl.nx) <= half_sm) ++pl.np;
+  } else {
+    // {ring, depth} wishes in priority order: activations must cover their load latency
+    // first (four atoms), then a third A stage decouples dequantisation from the MMA
+    const size_t budget = static_cast<size_t>(kSmemBudget);
+    const int wish[][2] = {{1, 4}, {0, 3}, {2, 3}, {2, 4}, {1, 6}, {2, 6}, {0, 4}, {1, 8}, {2, 8}};
+    for (const auto& w : wish) {
+      int na = pl.na, nx = pl.nx, np = pl.np;
+      (w[0] == 0 ? na : (w[0] == 1 ? nx : np)) = w[1];
+      if (na >= pl.na && nx >= pl.nx && np >= pl.np && total(np, na, nx) <= budget) {
+        pl.na = na;
+        pl.nx = nx;
+        pl.np = np;
+      }
+    }
   }
   pl.smem_bytes = total(pl.np, pl.na, pl.nx);
 
@@ -640,13 +835,30 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.np = pl.np;
   p.na = pl.na;
   p.nx = pl.nx;
+  p.static_weights = a.static_weights ? 1 : 0;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   p.status = reinterpret_cast<unsigned*>(ws);
   p.counters = reinterpret_cast<unsigned*>(ws + 256);
   p.partial = reinterpret_cast<float*>(ws + kWsHeaderBytes);
 
-  dim3 grid(pl.n_tiles, pl.m_tiles, pl.splits), block(kTcThreads);
-  wq_gemm_tc_kernel<FMT, T><<<grid, block, pl.smem_bytes, a.stream>>>(tm_w, tm_x, p);
+  // Programmatic dependent launch: this grid may begin its set-up (and, with static
+  // weights, its weight stream) while the previous kernel of the stream drains; the
+  // kernel orders itself with griddepcontrol.wait before touching x, y or the workspace.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(pl.n_tiles, pl.m_tiles, pl.splits);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T>, tm_w, tm_x, p);
+  if (e != cudaSuccess) {
+    set_last_error("cudaLaunchKernelEx", e);
+    return B200Q_ERR_CUDA;
+  }
   return note_launch();
 }
 

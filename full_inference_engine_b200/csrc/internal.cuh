@@ -31,6 +31,7 @@ struct ForwardArgs {
   int M, N, K;
   void* workspace;
   size_t workspace_bytes;
+  bool static_weights;  // weights/scales/zeros/bias were written long before this call
   cudaStream_t stream;
 };
 

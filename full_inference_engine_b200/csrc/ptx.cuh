@@ -59,6 +59,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking phase test (try_wait may suspend the thread for a while before it
+// answers "not yet"; a thread that services several barriers must not do that).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Polls at most `kMaxPolls` times.  try_wait itself suspends the thread for a
 // hardware-chosen interval, so the bound is of the order of a second.
 constexpr uint32_t kMaxPolls = 1u << 22;

@@ -18,7 +18,7 @@ from .w4a16_format import (  # noqa: F401  (re-exported like the reference modul
 _KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERNEL_TC}
 
 
-def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where):
+def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, static_weights=False):
     _lib.require_cuda(inputs, "inputs")
     m, k = inputs.shape
     n = packed.shape[0]
@@ -52,18 +52,23 @@ def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where):
             s.data_ptr(), None if z is None else z.data_ptr(), group_size,
             None if b is None else b.data_ptr(),
             out.data_ptr(), out.stride(0), m, n, k,
-            ws.data_ptr(), ws.numel(), kernel, _lib.stream_ptr(inputs.device)), where)
+            ws.data_ptr(), ws.numel(), kernel | (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0),
+            _lib.stream_ptr(inputs.device)), where)
     return out
 
 
 def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
                  bias: torch.Tensor | None = None, *, group_size: int = GROUP_SIZE,
                  block_m: int = 16, block_n: int = 64, num_warps: int = 4,
-                 kernel: str = "auto", zeros: torch.Tensor | None = None) -> torch.Tensor:
+                 kernel: str = "auto", zeros: torch.Tensor | None = None,
+                 static_weights: bool = False) -> torch.Tensor:
     """``inputs [M, K]`` x dequantised ``packed/scales`` -> ``[M, N]`` in ``inputs.dtype``.
 
     Reference: ``w4a16_linear`` (engine/kernels/w4a16_linear.py:77-117).  With ``zeros``
     the weights are the asymmetric int32 layout (``packed`` is ``[N, K//8] int32``).
+    ``static_weights=True`` promises that packed/scales/zeros/bias were not written by the
+    kernel just before this call in the stream (module buffers): the kernel may then read
+    them while that kernel is still finishing.
     """
     asym = zeros is not None
     want = torch.int32 if asym else torch.uint8
@@ -83,7 +88,8 @@ def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tenso
         raise ValueError("bias must have shape [N]")
     if block_m < 16 or block_n < 16:
         raise ValueError("tl.dot requires tiles of at least 16")
-    return _forward(inputs, packed, scales, zeros, bias, group_size, _KERNELS[kernel], "w4a16_linear")
+    return _forward(inputs, packed, scales, zeros, bias, group_size, _KERNELS[kernel], "w4a16_linear",
+                    static_weights)
 
 
 def w4a16_gemv(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,

@@ -44,11 +44,13 @@ def quantize_weight_per_channel_fp32_scales(weight: torch.Tensor) -> tuple[torch
 
 
 def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
-                 bias: torch.Tensor | None = None, *, kernel: str = "auto") -> torch.Tensor:
+                 bias: torch.Tensor | None = None, *, kernel: str = "auto",
+                 static_weights: bool = False) -> torch.Tensor:
     """W8A16 linear for 2-D activations (engine/kernels/w8a16_linear.py:50-69).
 
     The integer weights enter the multiply unscaled (they are exact in fp16 and bf16);
     the per-channel scale and the bias are applied to the fp32 accumulator.
+    ``static_weights``: see ``w4a16_linear``.
     """
     if inputs.ndim != 2 or qweight.ndim != 2 or qweight.dtype is not torch.int8:
         raise ValueError("inputs must be 2D and qweight must be 2D INT8")
@@ -83,6 +85,8 @@ def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tens
             w.data_ptr(), w.stride(0), s.data_ptr(), _lib.dtype_enum(s.dtype),
             None if b is None else b.data_ptr(),
             out.data_ptr(), out.stride(0), m, n, k,
-            ws.data_ptr(), ws.numel(), _KERNELS[kernel], _lib.stream_ptr(inputs.device)),
+            ws.data_ptr(), ws.numel(),
+            _KERNELS[kernel] | (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0),
+            _lib.stream_ptr(inputs.device)),
             "w8a16_linear")
     return out

@@ -60,6 +60,15 @@ typedef enum b200q_kernel {
   B200Q_KERNEL_TC = 2     /* tcgen05 tensor-core GEMM, weights on the M side   */
 } b200q_kernel;
 
+/* OR-ed into the `kernel` argument of a forward call.
+ * STATIC_WEIGHTS: the weights, scales, zero-points and bias of this call were last
+ * written before the PREVIOUS kernel of the stream was launched (module buffers
+ * set at install time).  The kernel may then start streaming them while that
+ * previous kernel is still draining (programmatic dependent launch); activations,
+ * outputs and the workspace always stay in stream order.  Without the flag
+ * everything stays in stream order.                                            */
+#define B200Q_FLAG_STATIC_WEIGHTS 0x100
+
 /* W8 quantizer flavours */
 typedef enum b200q_w8_mode {
   /* engine/kernels/w8a16_linear.py:43-47: scale = fp16(max|w|.clamp_min(1e-8)/127),
