@@ -23,7 +23,10 @@
 // Reference counterparts: _w4a16_linear_kernel (engine/kernels/w4a16_linear.py:27-74),
 // _w8a16_linear_kernel (engine/kernels/w8a16_linear.py:10-40) and the dense
 // dequantise-then-cuBLAS branch of W4A16Linear (engine/quantization/w4a16.py:158-178).
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "internal.cuh"
@@ -52,6 +55,7 @@ struct TcParams {
   int groups;        // K / 128 for the 4-bit formats
   int tok;           // tokens per tile
   int tmem_cols;
+  int a_col0;        // first TMEM column of the A operand stages (A-in-TMEM variant)
   uint32_t idesc;
   int kb_total;      // ceil(K / 128)
   int kb_per_split;
@@ -158,6 +162,56 @@ __device__ __forceinline__ __half pick_half(const uint4& v, int idx) {
   return __ushort_as_half(static_cast<unsigned short>((idx & 1) ? (w >> 16) : (w & 0xFFFFu)));
 }
 
+// Per-stage constants of one row's group, prepared once: subtrahends for the two nibble
+// encodings and the scale, as fp16x2 or bf16x2 bit patterns.
+struct PairConsts {
+  uint32_t bias_lo;    // 1024 + zero (fp16)  or 128 + zero (bf16)
+  uint32_t nbias_hi;   // -(64 + zero) (fp16) or -(8 + zero) (bf16): after the x1/16 of the high encoding
+  uint32_t scale;
+};
+
+// enc holds two encoded nibbles (kh = 0: magic + n; kh = 1: magic + 16 n).  Returns
+// (n - zero) * scale for both, in the operand dtype.
+template <bool BF16>
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t enc, int kh, const PairConsts& g) {
+  if (BF16) {
+    __nv_bfloat162 e = *reinterpret_cast<__nv_bfloat162*>(&enc);
+    const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(&g.scale);
+    __nv_bfloat162 c;
+    if (kh == 0) {
+      c = __hsub2(e, *reinterpret_cast<const __nv_bfloat162*>(&g.bias_lo));
+    } else {
+      // 128 + 16 n: times 1/16 is 8 + n, exact
+      c = __hfma2(e, __float2bfloat162_rn(0.0625f), *reinterpret_cast<const __nv_bfloat162*>(&g.nbias_hi));
+    }
+    c = __hmul2(c, s);
+    return *reinterpret_cast<uint32_t*>(&c);
+  } else {
+    __half2 e = as_h2(enc);
+    __half2 c;
+    if (kh == 0) {
+      c = __hsub2(e, as_h2(g.bias_lo));
+    } else {
+      c = __hfma2(e, __float2half2_rn(0.0625f), as_h2(g.nbias_hi));
+    }
+    c = __hmul2(c, as_h2(g.scale));
+    return as_u32(c);
+  }
+}
+
+// Low / high nibble pair of a 32-bit word laid out as (.., n_hi, n_lo, .., n_hi, n_lo).
+// fp16: 0x6400 | n = 1024 + n, and the high nibble in place is 1024 + 16 n.  bf16 has only
+// seven mantissa bits, so the high nibble is shifted down and encoded as 128 + n.
+template <bool BF16>
+__device__ __forceinline__ uint32_t deq_lo(uint32_t u, const PairConsts& g) {
+  return dequant_pair<BF16>(lop3_and_or(u, 0x000F000Fu, BF16 ? 0x43004300u : 0x64006400u), 0, g);
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t deq_hi(uint32_t u, const PairConsts& g) {
+  if (BF16) return dequant_pair<true>(lop3_and_or(u >> 4, 0x000F000Fu, 0x43004300u), 0, g);
+  return dequant_pair<false>(lop3_and_or(u, 0x00F000F0u, 0x64006400u), 1, g);
+}
+
 template <int FMT>
 __device__ __forceinline__ void load_group_chunk(GroupChunk& g, const TcParams& p, int chunk,
                                                  bool vec, int n0, int n1) {
@@ -180,8 +234,8 @@ __device__ __forceinline__ void load_group_chunk(GroupChunk& g, const TcParams& 
   }
 }
 
-template <int FMT, typename T>
-__global__ void __launch_bounds__(kTcThreads, 1)
+template <int FMT, typename T, bool ATM>
+__global__ void __launch_bounds__(kTcThreads, ATM ? 2 : 1)
 wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                   const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -189,7 +243,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int x_atom_bytes = p.tok * 128;                  // one 64-wide K atom of [tok x 128 B]
   const uint32_t a_ring = smem_base;
-  const uint32_t x_ring = a_ring + p.na * kStageBytesA;
+  const uint32_t x_ring = a_ring + (ATM ? 0 : p.na * kStageBytesA);
   const uint32_t p_ring = x_ring + p.nx * x_atom_bytes;
   const uint32_t bars = p_ring + p.np * PackedStage<FMT>::kBytes;
   // barrier slots (8 bytes each)
@@ -336,11 +390,17 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tc_fence_after_sync();
           const uint64_t adesc = umma_desc_sw128(a_stage + atom * kAtomBytesA);
           const uint64_t bdesc = umma_desc_sw128(x_ring + sx * x_atom_bytes);
+          // A in tensor memory: stage sa holds 128 K elements as 64 columns, 8 per MMA
+          const uint32_t a_tmem = tmem_base + p.a_col0 + sa * 64 + atom * 32;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // advance 16 elements = 32 bytes along K inside the swizzle atom
-            umma_f16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc,
-                        (i > 0 || atom > 0 || k > 0) ? 1u : 0u);
+            const uint32_t acc = (i > 0 || atom > 0 || k > 0) ? 1u : 0u;
+            if (ATM) {
+              umma_f16_ts(tmem_base, a_tmem + 8 * k, bdesc + 2 * k, p.idesc, acc);
+            } else {
+              umma_f16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc, acc);
+            }
           }
           umma_commit(x_empty + 8 * sx);
         }
@@ -356,7 +416,13 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int td = threadIdx.x - 64;          // 0..255
     const int q = td & 3;                      // 16-byte vector inside a 64-byte packed row
     const int r_base = td >> 2;                // 0..63
-    const int row_n0 = n_tile * kBlockN + r_base, row_n1 = row_n0 + 64;
+    // A-in-TMEM mapping: a warp may only touch TMEM lanes 32*(warp%4)..+31
+    const int atm_row = (warp & 3) * 32 + lane;
+    const int atm_kh = (warp - 2) >> 2;
+    const uint32_t atm_taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                               p.a_col0 + atm_kh * 32;
+    const int row_n0 = n_tile * kBlockN + (ATM ? atm_row : r_base);
+    const int row_n1 = ATM ? p.N : row_n0 + 64;
     const bool vec = (p.groups & 7) == 0;
     const int chunk_shift = vec ? 3 : 0;
     GroupChunk cur, nxt;
@@ -388,13 +454,103 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           nbias_hi[j] = __float2half2_rn(-(64.0f + zp));
         }
       }
-      ok = wait_or_abort(p_full + 8 * sp, (i / p.np) & 1, abort_p) &&
-           wait_or_abort(a_empty + 8 * sa, ((i / p.na) & 1) ^ 1, abort_p);
+      if (td == 0 && i == 3) B200Q_STAMP(5);
+      PairConsts gp{0u, 0u, 0u};
+      if (ATM && FMT != FMT_W8) {
+        const int idx = ((p.groups & 7) == 0) ? (kb & 7) : 0;
+        const __half sh = pick_half(cur.s[0], idx);
+        const float zp = (FMT == FMT_W4_ASYM) ? __half2float(pick_half(cur.z[0], idx)) : 8.0f;
+        if (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+          gp.bias_lo = as_u32(__float2bfloat162_rn(128.0f + zp));
+          gp.nbias_hi = as_u32(__float2bfloat162_rn(-(8.0f + zp)));
+          gp.scale = as_u32(__float2bfloat162_rn(__half2float(sh)));
+        } else {
+          gp.bias_lo = as_u32(__float2half2_rn(1024.0f + zp));
+          gp.nbias_hi = as_u32(__float2half2_rn(-(64.0f + zp)));
+          gp.scale = as_u32(__half2half2(sh));
+        }
+      }
+      ok = wait_or_abort(p_full + 8 * sp, (i / p.np) & 1, abort_p);
+      if (td == 0 && i == 3) B200Q_STAMP(6);
+      ok = ok && wait_or_abort(a_empty + 8 * sa, ((i / p.na) & 1) ^ 1, abort_p);
       if (!ok) break;
       if (td == 0 && i < 12) B200Q_STAMP(32 + 2 * i);
       const uint32_t p_stage = p_ring + sp * PackedStage<FMT>::kBytes;
       const uint32_t a_stage = a_ring + sa * kStageBytesA;
-      if (FMT == FMT_W4_REF) {
+      if (td == 0 && i == 3) B200Q_STAMP(7);
+      if (ATM) {
+        // One thread = one output channel (its TMEM lane) x one 64-wide half of the K block.
+        // The packed stage is read row-wise; the TMA 64-byte swizzle keeps that conflict-free.
+        const uint32_t prow = p_stage + (FMT == FMT_W8 ? atm_kh * (kBlockN * 64) : 0) + atm_row * 64;
+        const int xr = (atm_row >> 1) & 3;
+        uint32_t out[32];
+        // fp16 activations: (1024 + n) - (1024 + zero) is exact, then ONE fp16 multiply by the
+        // scale (the format's contract).  bf16 activations: the same in bf16, (128 + n) - (128 +
+        // zero) exact, one bf16 multiply by the scale rounded to bf16.
+        constexpr bool kBf = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+        if (FMT == FMT_W4_REF) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = ld_shared_v4(prow + ((c ^ xr) << 4));
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              // bytes (b0,b1,b2,b3) -> (b0,b2,b1,b3): the 0x000F000F / 0x00F000F0 masks then
+              // pick (b0,b1) from the word and (b2,b3) from the word shifted by 8
+              const uint32_t u = prmt(words[w], 0u, 0x3120);
+              if (atm_kh == 0) {
+                out[(c * 4 + w) * 2] = deq_lo<kBf>(u, gp);
+                out[(c * 4 + w) * 2 + 1] = deq_lo<kBf>(u >> 8, gp);
+              } else {
+                out[(c * 4 + w) * 2] = deq_hi<kBf>(u, gp);
+                out[(c * 4 + w) * 2 + 1] = deq_hi<kBf>(u >> 8, gp);
+              }
+            }
+          }
+        } else if (FMT == FMT_W4_ASYM) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const uint4 v = ld_shared_v4(prow + (((2 * atm_kh + c) ^ xr) << 4));
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const uint32_t word = words[w];
+              // byte k holds nibbles 2k (low) and 2k+1 (high).  Target halves:
+              //   (n0,n1) = (B0.lo, B0.hi)  (n2,n3) = (B1.lo, B1.hi) ...
+              // (B0.lo, B1.lo) = (n0,n2) and (B0.hi, B1.hi) = (n1,n3) come from one shuffled
+              // word; interleave the two results with a byte permute.
+              const uint32_t u = prmt(word, 0u, 0x3120);            // (B0,B2,B1,B3)
+              const uint32_t lo01 = deq_lo<kBf>(u, gp);        // n0,n2
+              const uint32_t hi01 = deq_hi<kBf>(u, gp);        // n1,n3
+              const uint32_t lo23 = deq_lo<kBf>(u >> 8, gp);   // n4,n6
+              const uint32_t hi23 = deq_hi<kBf>(u >> 8, gp);   // n5,n7
+              out[(c * 4 + w) * 4 + 0] = prmt(lo01, hi01, 0x5410);   // n0,n1
+              out[(c * 4 + w) * 4 + 1] = prmt(lo01, hi01, 0x7632);   // n2,n3
+              out[(c * 4 + w) * 4 + 2] = prmt(lo23, hi23, 0x5410);   // n4,n5
+              out[(c * 4 + w) * 4 + 3] = prmt(lo23, hi23, 0x7632);   // n6,n7
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = ld_shared_v4(prow + ((c ^ xr) << 4));
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              __half2 k01, k23;
+              int8x4_to_h2(words[w], k01, k23);
+              out[(c * 4 + w) * 2] = pack_operand<T>(k01);
+              out[(c * 4 + w) * 2 + 1] = pack_operand<T>(k23);
+            }
+          }
+        }
+        if (td == 0 && i == 3) B200Q_STAMP(61);
+        tmem_st_x32(atm_taddr + sa * 64, out);
+        if (td == 0 && i == 3) B200Q_STAMP(62);
+        tmem_st_wait();
+        if (td == 0 && i == 3) B200Q_STAMP(63);
+        tc_fence_before_sync();
+      } else if (FMT == FMT_W4_REF) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int row = r_base + 64 * j;
@@ -454,7 +610,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
       }
       // make the generic-proxy writes visible to the tensor core (async proxy)
-      fence_proxy_async_smem();
+      if (!ATM) fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(a_full + 8 * sa);
@@ -691,14 +847,26 @@ constexpr size_t kWsHeaderBytes = 64 * 1024;
 constexpr int kMaxSplitTiles = static_cast<int>((kWsHeaderBytes - 256) / sizeof(unsigned));
 
 struct TcPlan {
-  int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, tmem_cols;
+  int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, tmem_cols, a_col0;
+  bool atm;          // A operand in tensor memory (default) or in shared memory
   size_t smem_bytes;
 };
 
 static int packed_stage_bytes(int format) { return format == FMT_W8 ? kBlockN * 128 : kBlockN * 64; }
 
+// B200Q_TC_OPERAND=smem selects the variant that stages the dequantised A operand in
+// shared memory; the default keeps it in tensor memory.
+static bool use_tmem_operand() {
+  static const bool v = []() {
+    const char* e = std::getenv("B200Q_TC_OPERAND");
+    return !(e && std::strcmp(e, "smem") == 0);
+  }();
+  return v;
+}
+
 static TcPlan make_plan(int format, int M, int N, int K) {
   TcPlan pl{};
+  pl.atm = use_tmem_operand();
   const int mt = (M + 255) / 256;
   int tok = ((M + mt - 1) / mt + 15) / 16 * 16;
   if (tok < 16) tok = 16;
@@ -706,39 +874,70 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   pl.m_tiles = (M + tok - 1) / tok;
   pl.n_tiles = (N + kBlockN - 1) / kBlockN;
   pl.kb_total = (K + kBlockK - 1) / kBlockK;
-  int cols = 32;
-  while (cols < tok) cols <<= 1;
-  pl.tmem_cols = cols;
 
-  // Ring depths.  Narrow token tiles are the HBM-bound regime: keep a block under half an
-  // SM's shared memory so that two blocks are resident and one block's set-up and epilogue
-  // overlap the other's weight stream.  Wide tiles take the whole SM and deeper rings.
   const int pbytes = packed_stage_bytes(format);
   const int xbytes = tok * 128;                    // one activation atom
+  const size_t a_stage_smem = pl.atm ? 0 : kStageBytesA;
   auto total = [&](int np, int na, int nx) {
-    return static_cast<size_t>(na) * kStageBytesA + static_cast<size_t>(nx) * xbytes +
+    return static_cast<size_t>(na) * a_stage_smem + static_cast<size_t>(nx) * xbytes +
            static_cast<size_t>(np) * pbytes + 1024 /*alignment*/ + 8 * kMaxRing * 6 + 64;
   };
   const size_t half_sm = 115712;                   // (228 KiB - 2 x 1 KiB reserved) / 2
-  const bool two_per_sm = tok <= 32 && total(2, 2, 4) <= half_sm;
+  const size_t budget = static_cast<size_t>(kSmemBudget);
+  bool two_per_sm;
   pl.na = 2;
   pl.nx = 2;
   pl.np = 2;
-  if (two_per_sm) {
-    pl.nx = 4;
-    while (pl.np < kMaxRing && total(pl.np + 1, pl.na, pl.nx) <= half_sm) ++pl.np;
+  if (pl.atm) {
+    // TMEM columns: accumulator [0, tok), then `na` operand stages of 64 columns each.
+    // Two resident blocks need <= 256 columns each: narrow tiles (decode, HBM-bound) take
+    // that shape so one block's set-up and epilogue overlap the other's weight stream.
+    pl.a_col0 = (tok + 63) / 64 * 64;
+    two_per_sm = tok <= 64 && total(4, 0, 4) <= half_sm;
+    if (two_per_sm) {
+      pl.na = (256 - pl.a_col0) / 64;              // 3 for tok <= 64
+      pl.nx = 4;
+      pl.np = 4;
+      while (pl.np < kMaxRing && total(pl.np + 1, 0, pl.nx) <= half_sm) ++pl.np;
+      pl.tmem_cols = 256;
+    } else {
+      pl.na = (512 - pl.a_col0) / 64;
+      if (pl.na > 4) pl.na = 4;
+      pl.nx = 4;
+      pl.np = 3;
+      const int wish[][2] = {{1, 6}, {2, 4}, {2, 6}, {1, 8}, {2, 8}};
+      for (const auto& w : wish) {
+        int nx = pl.nx, np = pl.np;
+        (w[0] == 1 ? nx : np) = w[1];
+        if (nx >= pl.nx && np >= pl.np && total(np, 0, nx) <= budget) {
+          pl.nx = nx;
+          pl.np = np;
+        }
+      }
+      while (total(pl.np, 0, pl.nx) > budget && pl.nx > 2) --pl.nx;
+      pl.tmem_cols = 512;
+    }
   } else {
-    // {ring, depth} wishes in priority order: activations must cover their load latency
-    // first (four atoms), then a third A stage decouples dequantisation from the MMA
-    const size_t budget = static_cast<size_t>(kSmemBudget);
-    const int wish[][2] = {{1, 4}, {0, 3}, {2, 3}, {2, 4}, {1, 6}, {2, 6}, {0, 4}, {1, 8}, {2, 8}};
-    for (const auto& w : wish) {
-      int na = pl.na, nx = pl.nx, np = pl.np;
-      (w[0] == 0 ? na : (w[0] == 1 ? nx : np)) = w[1];
-      if (na >= pl.na && nx >= pl.nx && np >= pl.np && total(np, na, nx) <= budget) {
-        pl.na = na;
-        pl.nx = nx;
-        pl.np = np;
+    int cols = 32;
+    while (cols < tok) cols <<= 1;
+    pl.tmem_cols = cols;
+    pl.a_col0 = 0;
+    two_per_sm = tok <= 32 && total(2, 2, 4) <= half_sm;
+    if (two_per_sm) {
+      pl.nx = 4;
+      while (pl.np < kMaxRing && total(pl.np + 1, pl.na, pl.nx) <= half_sm) ++pl.np;
+    } else {
+      // {ring, depth} wishes in priority order: activations must cover their load latency
+      // first (four atoms), then a third A stage decouples dequantisation from the MMA
+      const int wish[][2] = {{1, 4}, {0, 3}, {2, 3}, {2, 4}, {1, 6}, {2, 6}, {0, 4}, {1, 8}, {2, 8}};
+      for (const auto& w : wish) {
+        int na = pl.na, nx = pl.nx, np = pl.np;
+        (w[0] == 0 ? na : (w[0] == 1 ? nx : np)) = w[1];
+        if (na >= pl.na && nx >= pl.nx && np >= pl.np && total(np, na, nx) <= budget) {
+          pl.na = na;
+          pl.nx = nx;
+          pl.np = np;
+        }
       }
     }
   }
@@ -784,7 +983,7 @@ bool tc_supported(const ForwardArgs& a) {
   return true;
 }
 
-template <int FMT, typename T>
+template <int FMT, typename T, bool ATM>
 static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   static bool attr_set_dev[64] = {};
   static std::mutex attr_mu;
@@ -794,7 +993,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
     bool& attr_set = attr_set_dev[dev & 63];
     std::lock_guard<std::mutex> g(attr_mu);
     if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(wq_gemm_tc_kernel<FMT, T>,
+      cudaError_t e = cudaFuncSetAttribute(wq_gemm_tc_kernel<FMT, T, ATM>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
       if (e != cudaSuccess) {
         set_last_error("cudaFuncSetAttribute", e);
@@ -805,8 +1004,10 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   }
   CUtensorMap tm_w, tm_x;
   const uint64_t w_cols = (FMT == FMT_W8) ? static_cast<uint64_t>(a.K) : static_cast<uint64_t>(a.K / 2);
+  // the A-in-TMEM variant reads the packed stage one row per thread: 64-byte swizzle
   if (!get_tensor_map(&tm_w, a.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_cols, static_cast<uint64_t>(a.N),
-                      static_cast<uint64_t>(a.ldw), 64, kBlockN, CU_TENSOR_MAP_SWIZZLE_NONE))
+                      static_cast<uint64_t>(a.ldw), 64, kBlockN,
+                      ATM ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE))
     return B200Q_ERR_CUDA;
   const CUtensorMapDataType xdt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -828,6 +1029,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.groups = (FMT == FMT_W8) ? 1 : a.K / 128;
   p.tok = pl.tok;
   p.tmem_cols = pl.tmem_cols;
+  p.a_col0 = pl.a_col0;
   p.idesc = umma_idesc_f16(a.act_dtype == B200Q_F16 ? 0u : 1u, 128u, static_cast<uint32_t>(pl.tok));
   p.kb_total = pl.kb_total;
   p.kb_per_split = pl.kb_per_split;
@@ -854,12 +1056,17 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T>, tm_w, tm_x, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T, ATM>, tm_w, tm_x, p);
   if (e != cudaSuccess) {
     set_last_error("cudaLaunchKernelEx", e);
     return B200Q_ERR_CUDA;
   }
   return note_launch();
+}
+
+template <int FMT, typename T>
+static int launch_tc_operand(const ForwardArgs& a, const TcPlan& pl) {
+  return pl.atm ? launch_tc_typed<FMT, T, true>(a, pl) : launch_tc_typed<FMT, T, false>(a, pl);
 }
 
 int launch_forward_tc(const ForwardArgs& a) {
@@ -872,13 +1079,13 @@ int launch_forward_tc(const ForwardArgs& a) {
   const bool h = a.act_dtype == B200Q_F16;
   switch (a.format) {
     case FMT_W8:
-      return h ? launch_tc_typed<FMT_W8, __half>(a, pl) : launch_tc_typed<FMT_W8, __nv_bfloat16>(a, pl);
+      return h ? launch_tc_operand<FMT_W8, __half>(a, pl) : launch_tc_operand<FMT_W8, __nv_bfloat16>(a, pl);
     case FMT_W4_REF:
-      return h ? launch_tc_typed<FMT_W4_REF, __half>(a, pl)
-               : launch_tc_typed<FMT_W4_REF, __nv_bfloat16>(a, pl);
+      return h ? launch_tc_operand<FMT_W4_REF, __half>(a, pl)
+               : launch_tc_operand<FMT_W4_REF, __nv_bfloat16>(a, pl);
     case FMT_W4_ASYM:
-      return h ? launch_tc_typed<FMT_W4_ASYM, __half>(a, pl)
-               : launch_tc_typed<FMT_W4_ASYM, __nv_bfloat16>(a, pl);
+      return h ? launch_tc_operand<FMT_W4_ASYM, __half>(a, pl)
+               : launch_tc_operand<FMT_W4_ASYM, __nv_bfloat16>(a, pl);
     default:
       return B200Q_ERR_INVALID;
   }
