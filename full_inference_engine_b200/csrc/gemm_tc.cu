@@ -358,9 +358,14 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
         if (progress) {
           idle = 0;
-        } else if (++idle > (kMaxPolls << 4) || ((idle & 0x3FF) == 0 && *abort_p)) {
-          ok = false;
-          break;
+        } else {
+          // nothing to do: step aside so this poll loop does not take issue slots from the
+          // dequantising warps that share the scheduler
+          __nanosleep(64);
+          if (++idle > kMaxPolls || ((idle & 0x3FF) == 0 && *abort_p)) {
+            ok = false;
+            break;
+          }
         }
       }
       B200Q_STAMP(4);
