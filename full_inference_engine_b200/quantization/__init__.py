@@ -1,0 +1,13 @@
+"""Quantized ``nn.Linear`` replacements over the B200 kernels (mirrors ``engine/quantization``)."""
+
+from .int8 import Int8Linear, model_storage_bytes, quantize_linear_modules
+from .w4a16 import (
+    W4A16Linear, W4A16Report, describe, install_w4a16, load_w4a16_model, reference_mode,
+    w4a16_modules,
+)
+
+__all__ = [
+    "Int8Linear", "model_storage_bytes", "quantize_linear_modules",
+    "W4A16Linear", "W4A16Report", "describe", "install_w4a16", "load_w4a16_model",
+    "reference_mode", "w4a16_modules",
+]
