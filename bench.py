@@ -354,6 +354,10 @@ def run_b200(args, cases):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    def note(msg):
+        if args.verbose:
+            print(f"# rank {rank}: {msg}", file=sys.stderr, flush=True)
+
     pk = peaks()
     copies = 10 if args.workload in ("c2", "c1") else (4 if args.workload == "c4" else 3)
     weight_sets = make_weight_sets(cases, copies, device, rank, world)
@@ -380,98 +384,13 @@ def run_b200(args, cases):
                 f"between reuses (L2 = 126 MiB)")
 
     # eager warm-up (also sizes the workspace), then capture two step variants
+    note("inputs ready")
     for v in (0, 1):
         one_step(v)
     torch.cuda.synchronize()
-    launches_before = _lib.launch_count()
-    graphs = []
-    use_graph = True
-    try:
-        for v in (0, 1):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                one_step(v)
-            graphs.append(g)
-    except Exception as exc:      # NCCL capture unsupported etc.: time eager launches instead
-        use_graph = False
-        graphs = []
-        torch.cuda.synchronize()
-        if rank == 0:
-            print(f"# graph capture failed ({exc}); timing eager launches", file=sys.stderr)
-    launches_per_step = (_lib.launch_count() - launches_before) // 2 if use_graph else len(cases)
+    note("eager warm-up done")
 
-    def run_step(i):
-        if use_graph:
-            graphs[i & 1].replay()
-        else:
-            one_step(i & 1)
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    # bring the clocks up, then the requested warm-up steps
-    t_end = time.perf_counter() + 0.3
-    i = 0
-    while time.perf_counter() < t_end:
-        run_step(i)
-        i += 1
-        if i % 64 == 0:
-            torch.cuda.synchronize()
-    for j in range(max(3, args.warmup)):
-        run_step(j)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for j in range(args.steps):
-        run_step(j)
-    end.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-    ms_total = start.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([ms_total], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-
-    # ---- per-case latency (roofline): R back-to-back launches over rotating weight copies
-    per_case = []
-    for i, case in enumerate(local_cases):
-        sets = weight_sets[(case.fmt, case.name)]
-        reps = len(sets)
-        for w in sets[:2]:
-            forward(case, acts[i], w)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for w in sets:
-                forward(case, acts[i], w)
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        times = []
-        for _ in range(7):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            g.replay()
-            e.record()
-            torch.cuda.synchronize()
-            times.append(s.elapsed_time(e) / reps)
-        sec = statistics.median(times) * 1e-3
-        entry = {"case": case.key, "M": case.m, "K": case.k, "N": case.n, "us": round(sec * 1e6, 2),
-                 "GBps": round(case.bytes / sec / 1e9, 1), "TFLOPs": round(case.flops / sec / 1e12, 2)}
-        entry.update(roofline_entry(case, sec, pk))
-        entry["frac_of_nominal"] = round(
-            max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
-        per_case.append(entry)
-        del g
-    clocks = sampler.stop()
-
-    # ---- end to end: pinned host activations in, host results out, through the public API
+    # ---- end to end (measured before any graph holds NCCL work): pinned host activations in, host results out, through the public API
     host_x = [torch.empty(c.m, c.k, dtype=c.dtype).pin_memory().copy_(acts[i].cpu()) for i, c in enumerate(cases)]
     host_y = [torch.empty(c.m, c.n // world, dtype=c.dtype).pin_memory() for c in cases]
     dev_x = [torch.empty_like(a) for a in acts]
@@ -505,12 +424,105 @@ def run_b200(args, cases):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
 
+    note(f"e2e done: {e2e_ms:.4f} ms/step")
+
+    launches_before = _lib.launch_count()
+    graphs = []
+    use_graph = True
+    try:
+        for v in (0, 1):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                one_step(v)
+            graphs.append(g)
+    except Exception as exc:      # NCCL capture unsupported etc.: time eager launches instead
+        use_graph = False
+        graphs = []
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(f"# graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+    launches_per_step = (_lib.launch_count() - launches_before) // 2 if use_graph else len(cases)
+    note(f"capture done (graph={use_graph})")
+
+    def run_step(i):
+        if use_graph:
+            graphs[i & 1].replay()
+        else:
+            one_step(i & 1)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    # bring the clocks up, then the requested warm-up steps.  A FIXED count: with more than
+    # one rank every rank must issue the same number of collectives.
+    for i in range(256):
+        run_step(i)
+        if i % 64 == 63:
+            torch.cuda.synchronize()
+    for j in range(max(3, args.warmup)):
+        run_step(j)
+    torch.cuda.synchronize()
+    note("warm-up replays done")
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for j in range(args.steps):
+        run_step(j)
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms_total = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms_total], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    note(f"timed region done: {ms_step:.4f} ms/step")
+
+    # ---- per-case latency (roofline): R back-to-back launches over rotating weight copies
+    per_case = []
+    # per-case latencies are a single-GPU diagnostic; the multi-rank run reports the step only
+    for i, case in enumerate(local_cases if world == 1 else []):
+        sets = weight_sets[(case.fmt, case.name)]
+        reps = len(sets)
+        for w in sets[:2]:
+            forward(case, acts[i], w)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for w in sets:
+                forward(case, acts[i], w)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) / reps)
+        sec = statistics.median(times) * 1e-3
+        entry = {"case": case.key, "M": case.m, "K": case.k, "N": case.n, "us": round(sec * 1e6, 2),
+                 "GBps": round(case.bytes / sec / 1e9, 1), "TFLOPs": round(case.flops / sec / 1e12, 2)}
+        entry.update(roofline_entry(case, sec, pk))
+        entry["frac_of_nominal"] = round(
+            max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
+        per_case.append(entry)
+        del g
+    clocks = sampler.stop()
+    note("per-case timing done")
+
     status = _lib.library().b200q_workspace_status(_lib.workspace_for(device, 256).data_ptr(), None)
 
     if rank == 0:
         total_bytes = sum(c.bytes for c in cases)          # whole job, all ranks
         total_flops = sum(c.flops for c in cases)
-        dominant = max(per_case, key=lambda r: r["us"])
+        dominant = max(per_case, key=lambda r: r["us"]) if per_case else None
         step_us = sum(r["us"] for r in per_case)
         line = {
             "metric": METRIC, "value": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "unit": "GB/s",
@@ -519,9 +531,9 @@ def run_b200(args, cases):
             "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16/bf16 activations, fp32 accumulate", "data": "synthetic",
             "config": config_dict(args, cases, rotation),
-            "roofline": {k: dominant[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
-            | {"kernel": dominant["case"], "share_of_step": round(dominant["us"] / step_us, 3),
-               "peak_source": pk["source"]},
+            "roofline": ({k: dominant[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
+                         | {"kernel": dominant["case"], "share_of_step": round(dominant["us"] / step_us, 3),
+                            "peak_source": pk["source"]}) if dominant else None,
             "per_case": per_case,
             "clocks": clocks,
             "e2e": {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
@@ -541,8 +553,14 @@ def run_b200(args, cases):
                                     "ms_per_step": round(sec * 1e3, 2)}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # leave without further collectives: tear the communicator down from a helper thread
+        # and exit even if that blocks (every rank has synchronised its device by now)
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        closer = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        closer.start()
+        closer.join(timeout=10.0)
+        os._exit(0)
 
 
 def run_profile(args, cases):
@@ -570,6 +588,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c4", "c5"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
+    ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--profile", action="store_true",
                     help="eager launches of the selected cases only (for ncu): no graphs, no e2e, no CPU leg")
     args = ap.parse_args()

@@ -36,9 +36,10 @@ def _worker(rank, world, port, result):
                 out = shard(x)
                 single = full(x)
                 assert out.shape == single.shape
-                # the same kernel arithmetic per channel; split-K plans may differ with N
+                # the same kernel arithmetic per channel; split-K plans may differ with N, so
+                # an element may land on the neighbouring bf16 value (one ulp = 2^-8 relative)
                 assert float((out.float() - single.float()).abs().max()) <= \
-                    2e-3 * float(single.float().abs().max())
+                    2.0 ** -7 * float(single.float().abs().max())
         result[rank] = 1
     finally:
         dist.destroy_process_group()
