@@ -47,6 +47,10 @@ _SIGNATURES = {
     "b200q_w4a16_forward": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_int, _c_void_p,
                                      _c_void_p, _c_int, _c_void_p, _c_void_p, _c_i64, _c_int, _c_int,
                                      _c_int, _c_void_p, _c_size, _c_int, _c_void_p]),
+    "b200q_static_scratch_bytes": (_c_size, []),
+    "b200q_w4a16_forward_static_scratch": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_int,
+                                                    _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                                    _c_i64, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
 }
 
 _lib = None

@@ -182,6 +182,37 @@ int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype,
                         void* workspace, size_t workspace_bytes,
                         int kernel, void* stream);
 
+/*
+ * The INT4 forward for callers that have no device memory to give: same
+ * arguments and results as b200q_w4a16_forward, minus the workspace.  It has no
+ * counterpart in the reference.  It exists for hosts that cannot allocate on the
+ * GPU at the point of the call: an engine that has already handed all free HBM
+ * to its KV-cache pool, or a binding whose runtime passes it nothing but input
+ * and output pointers and forbids cudaMalloc (which would stall the device
+ * mid-serving).  The split-K scratch is a fixed array inside the library image
+ * (b200q_static_scratch_bytes(), 16 MiB, resident on every GPU that loads the
+ * library until the process exits); nothing is allocated, by this call or by
+ * anything it calls.
+ *
+ *  - Geometries whose b200q_workspace_bytes() exceeds the array are refused with
+ *    B200Q_ERR_WORKSPACE (b200q_last_error() names both sizes).
+ *  - The first call on each device looks up the array's device address and clears
+ *    its 64 KiB header with a synchronous cudaMemset: make that first call before
+ *    starting any stream capture on that device.
+ *  - All calls on a device share the one array and it keeps what the last call
+ *    left in it (the kernels return its counters to zero themselves).  Calls that
+ *    overlap on the GPU — different streams, or b200q_w4a16_forward given this same
+ *    memory — race on it: keep them in one stream order.
+ */
+size_t b200q_static_scratch_bytes(void);
+int b200q_w4a16_forward_static_scratch(const void* x, int64_t ldx, int act_dtype,
+                                       const void* packed, int64_t ldw, int layout,
+                                       const void* scales, const void* zeros, int group,
+                                       const void* bias,
+                                       void* y, int64_t ldy,
+                                       int M, int N, int K,
+                                       int kernel, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
