@@ -66,8 +66,10 @@ __device__ __forceinline__ W4Quad dequant_w4_word_splithalf(uint32_t w, __half2 
   return q;
 }
 
-// One 32-bit word of the sequential layout: nibble i is input 8w+i.  Produces
-// the eight weights in K order as four fp16x2, scaled.
+// One 32-bit word of the asymmetric layout.  Its eight nibbles hold inputs 8w+{0,2,4,6,1,3,5,7}
+// (input i sits at nibble position (i & 1) * 4 + (i >> 1)): the two 0x000F000F-spaced nibbles
+// that one lop3 isolates are then neighbours in K, so no byte permute is needed.  Produces the
+// eight weights in K order as four fp16x2, scaled.
 struct W4Oct {
   __half2 k01, k23, k45, k67;
 };
@@ -76,19 +78,11 @@ __device__ __forceinline__ W4Oct dequant_w4_word_seq(uint32_t w, __half2 bias_lo
   const uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u, kMagic = 0x64006400u;
   const __half2 sixteenth = __float2half2_rn(0.0625f);
   uint32_t w8 = w >> 8;
-  __half2 n04 = __hsub2(as_h2(lop3_and_or(w, kLoMask, kMagic)), bias_lo);       // nibbles 0,4
-  __half2 n15 = __hfma2(as_h2(lop3_and_or(w, kHiMask, kMagic)), sixteenth, neg_bias_hi);  // 1,5
-  __half2 n26 = __hsub2(as_h2(lop3_and_or(w8, kLoMask, kMagic)), bias_lo);      // 2,6
-  __half2 n37 = __hfma2(as_h2(lop3_and_or(w8, kHiMask, kMagic)), sixteenth, neg_bias_hi);  // 3,7
-  n04 = __hmul2(n04, scale);
-  n15 = __hmul2(n15, scale);
-  n26 = __hmul2(n26, scale);
-  n37 = __hmul2(n37, scale);
   W4Oct o;
-  o.k01 = as_h2(prmt(as_u32(n04), as_u32(n15), 0x5410));
-  o.k23 = as_h2(prmt(as_u32(n26), as_u32(n37), 0x5410));
-  o.k45 = as_h2(prmt(as_u32(n04), as_u32(n15), 0x7632));
-  o.k67 = as_h2(prmt(as_u32(n26), as_u32(n37), 0x7632));
+  o.k01 = __hmul2(__hsub2(as_h2(lop3_and_or(w, kLoMask, kMagic)), bias_lo), scale);
+  o.k23 = __hmul2(__hfma2(as_h2(lop3_and_or(w, kHiMask, kMagic)), sixteenth, neg_bias_hi), scale);
+  o.k45 = __hmul2(__hsub2(as_h2(lop3_and_or(w8, kLoMask, kMagic)), bias_lo), scale);
+  o.k67 = __hmul2(__hfma2(as_h2(lop3_and_or(w8, kHiMask, kMagic)), sixteenth, neg_bias_hi), scale);
   return o;
 }
 

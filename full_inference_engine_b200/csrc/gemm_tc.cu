@@ -23,6 +23,7 @@
 // Reference counterparts: _w4a16_linear_kernel (engine/kernels/w4a16_linear.py:27-74),
 // _w8a16_linear_kernel (engine/kernels/w8a16_linear.py:10-40) and the dense
 // dequantise-then-cuBLAS branch of W4A16Linear (engine/quantization/w4a16.py:158-178).
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -41,7 +42,7 @@ constexpr int kBlockN = 128;                 // output channels per block (UMMA 
 constexpr int kBlockK = 128;                 // K elements per pipeline step
 constexpr int kAtomBytesA = kBlockN * 128;   // one 64-wide K atom of the A operand: 16 KB
 constexpr int kStageBytesA = 2 * kAtomBytesA;
-constexpr int kMaxRing = 8;
+constexpr int kMaxRing = 16;
 constexpr int kSmemBudget = 226 * 1024;      // dynamic shared memory we ask for at most
 
 struct TcParams {
@@ -60,7 +61,8 @@ struct TcParams {
   int kb_total;      // ceil(K / 128)
   int kb_per_split;
   int splits;
-  int np, na, nx;    // ring depths
+  int np, na, nx;    // ring depths: weight groups, operand stages, activation chunks
+  int pg, xg;        // K blocks per weight group / per activation chunk (one TMA each)
   float* partial;    // [splits, M, N] fp32 (split-K only)
   int static_weights;  // weights/scales/bias may be read ahead of the stream order
   unsigned* counters;  // [m_tiles * n_tiles], zero between launches
@@ -244,8 +246,10 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const int x_atom_bytes = p.tok * 128;                  // one 64-wide K atom of [tok x 128 B]
   const uint32_t a_ring = smem_base;
   const uint32_t x_ring = a_ring + (ATM ? 0 : p.na * kStageBytesA);
-  const uint32_t p_ring = x_ring + p.nx * x_atom_bytes;
-  const uint32_t bars = p_ring + p.np * PackedStage<FMT>::kBytes;
+  const int x_chunk_bytes = p.xg * 2 * x_atom_bytes;     // xg K blocks of two atoms each
+  const int p_group_bytes = p.pg * PackedStage<FMT>::kBytes;
+  const uint32_t p_ring = x_ring + p.nx * x_chunk_bytes;
+  const uint32_t bars = p_ring + p.np * p_group_bytes;
   // barrier slots (8 bytes each)
   const uint32_t p_full = bars;
   const uint32_t p_empty = p_full + 8 * kMaxRing;
@@ -316,43 +320,50 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // One thread feeds two independent rings, polling whichever has a free slot: packed
     // weights (one stage per K block) and activations (one 64-wide atom per slot).
     if (elect_one()) {
-      int ip = 0, ix = 0;                       // weight stages / activation atoms issued
-      const int nx_total = 2 * nkb;
+      // ring positions are advanced incrementally (slot, phase): no division in the loops
+      int ip = 0, ix = 0;                       // weight groups / activation chunks issued
+      int sp = 0, sx = 0;                       // their ring slots
+      uint32_t p_phase = 1, x_phase = 1;        // parity to wait for on the empty barriers
+      const int np_total = (nkb + p.pg - 1) / p.pg;
+      const int nx_total = (nkb + p.xg - 1) / p.xg;
       bool waited = !p.static_weights;
       bool ok = true;
       uint32_t idle = 0;
-      while (ip < nkb || ix < nx_total) {
+      while (ip < np_total || ix < nx_total) {
         bool progress = false;
-        if (ip < nkb) {
-          const int sp = ip % p.np;
-          if (mbar_test_wait(p_empty + 8 * sp, ((ip / p.np) & 1) ^ 1)) {
-            const int kb = kb0 + ip;
-            const uint32_t pdst = p_ring + sp * PackedStage<FMT>::kBytes;
-            mbar_arrive_expect_tx(p_full + 8 * sp, PackedStage<FMT>::kBytes);
-            if (FMT == FMT_W8) {
-              tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 128, n_tile * kBlockN);
-              tma_load_2d(pdst + kBlockN * 64, &tm_w, p_full + 8 * sp, kb * 128 + 64, n_tile * kBlockN);
-            } else {
-              tma_load_2d(pdst, &tm_w, p_full + 8 * sp, kb * 64, n_tile * kBlockN);
-            }
+        if (ip < np_total) {
+          if (mbar_test_wait(p_empty + 8 * sp, p_phase)) {
+            // one instruction brings pg K blocks: [pg (x2 for int8)] x [128 rows] x [64 B]
+            const int kb = kb0 + ip * p.pg;
+            mbar_arrive_expect_tx(p_full + 8 * sp, static_cast<uint32_t>(p_group_bytes));
+            tma_load_3d(p_ring + sp * p_group_bytes, &tm_w, p_full + 8 * sp, 0, n_tile * kBlockN,
+                        (FMT == FMT_W8) ? 2 * kb : kb);
             if (ip == 0) B200Q_STAMP(3);
             ++ip;
+            if (++sp == p.np) {
+              sp = 0;
+              p_phase ^= 1;
+            }
             progress = true;
           }
         }
-        if (!waited && (ip >= nkb || ip >= p.np)) {
+        if (!waited && (ip >= np_total || ip >= p.np)) {
           // the weight ring is as far ahead as it can get: now order behind the stream
           grid_dependency_wait();
           waited = true;
           progress = true;
         }
         if (waited && ix < nx_total) {
-          const int sx = ix % p.nx;
-          if (mbar_test_wait(x_empty + 8 * sx, ((ix / p.nx) & 1) ^ 1)) {
-            mbar_arrive_expect_tx(x_full + 8 * sx, static_cast<uint32_t>(x_atom_bytes));
-            tma_load_2d(x_ring + sx * x_atom_bytes, &tm_x, x_full + 8 * sx,
-                        (kb0 + (ix >> 1)) * kBlockK + 64 * (ix & 1), m_tile * p.tok);
+          if (mbar_test_wait(x_empty + 8 * sx, x_phase)) {
+            // xg K blocks of activations: [2 xg atoms] x [tok rows] x [64 elements]
+            mbar_arrive_expect_tx(x_full + 8 * sx, static_cast<uint32_t>(x_chunk_bytes));
+            tma_load_3d(x_ring + sx * x_chunk_bytes, &tm_x, x_full + 8 * sx, 0, m_tile * p.tok,
+                        2 * (kb0 + ix * p.xg));
             ++ix;
+            if (++sx == p.nx) {
+              sx = 0;
+              x_phase ^= 1;
+            }
             progress = true;
           }
         }
@@ -380,21 +391,23 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       bool ok = true;
+      int sa = 0, sx = 0, xs = 0;                // operand stage, activation chunk slot, block in chunk
+      uint32_t a_phase = 0, x_phase = 0;
       for (int i = 0; i < nkb && ok; ++i) {
-        const int sa = i % p.na;
-        ok = wait_or_abort(a_full + 8 * sa, (i / p.na) & 1, abort_p);
+        if (xs == 0) {
+          ok = wait_or_abort(x_full + 8 * sx, x_phase, abort_p);
+          if (!ok) break;
+        }
+        ok = wait_or_abort(a_full + 8 * sa, a_phase, abort_p);
         if (!ok) break;
-        if (i < 12) B200Q_STAMP(8 + 2 * i);
+        tc_fence_after_sync();
+        if (i < 6) B200Q_STAMP(8 + 2 * i);
         const uint32_t a_stage = a_ring + sa * kStageBytesA;
+        const uint32_t x_stage = x_ring + sx * x_chunk_bytes + xs * 2 * x_atom_bytes;
 #pragma unroll
         for (int atom = 0; atom < 2; ++atom) {
-          const int xi = 2 * i + atom;
-          const int sx = xi % p.nx;
-          ok = wait_or_abort(x_full + 8 * sx, (xi / p.nx) & 1, abort_p);
-          if (!ok) break;
-          tc_fence_after_sync();
           const uint64_t adesc = umma_desc_sw128(a_stage + atom * kAtomBytesA);
-          const uint64_t bdesc = umma_desc_sw128(x_ring + sx * x_atom_bytes);
+          const uint64_t bdesc = umma_desc_sw128(x_stage + atom * x_atom_bytes);
           // A in tensor memory: stage sa holds 128 K elements as 64 columns, 8 per MMA
           const uint32_t a_tmem = tmem_base + p.a_col0 + sa * 64 + atom * 32;
 #pragma unroll
@@ -407,11 +420,21 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               umma_f16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc, acc);
             }
           }
-          umma_commit(x_empty + 8 * sx);
         }
-        if (!ok) break;
         umma_commit(a_empty + 8 * sa);
-        if (i < 12) B200Q_STAMP(9 + 2 * i);
+        if (xs == p.xg - 1 || i == nkb - 1) umma_commit(x_empty + 8 * sx);
+        if (i < 6) B200Q_STAMP(9 + 2 * i);
+        if (++sa == p.na) {
+          sa = 0;
+          a_phase ^= 1;
+        }
+        if (++xs == p.xg) {
+          xs = 0;
+          if (++sx == p.nx) {
+            sx = 0;
+            x_phase ^= 1;
+          }
+        }
       }
       if (!ok) flag_failure(abort_p, p.status, 2u);
       umma_commit(acc_full);
@@ -424,8 +447,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     // A-in-TMEM mapping: a warp may only touch TMEM lanes 32*(warp%4)..+31
     const int atm_row = (warp & 3) * 32 + lane;
     const int atm_kh = (warp - 2) >> 2;
-    const uint32_t atm_taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                               p.a_col0 + atm_kh * 32;
+    const uint32_t atm_taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + p.a_col0;
     const int row_n0 = n_tile * kBlockN + (ATM ? atm_row : r_base);
     const int row_n1 = ATM ? p.N : row_n0 + 64;
     const bool vec = (p.groups & 7) == 0;
@@ -438,9 +460,10 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (cur_chunk < last_chunk) load_group_chunk<FMT>(nxt, p, cur_chunk + 1, vec, row_n0, row_n1);
     }
     bool ok = true;
+    int sp = 0, ps = 0, sa = 0;                  // weight group slot, block in group, operand stage
+    uint32_t p_phase = 0, a_phase = 1;           // parities: p_full, a_empty
     for (int i = 0; i < nkb && ok; ++i) {
       const int kb = kb0 + i;
-      const int sp = i % p.np, sa = i % p.na;
       __half2 scale2[2];
       __half2 bias_lo[2], nbias_hi[2];
       if (FMT != FMT_W8) {
@@ -475,12 +498,12 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           gp.scale = as_u32(__half2half2(sh));
         }
       }
-      ok = wait_or_abort(p_full + 8 * sp, (i / p.np) & 1, abort_p);
+      if (ps == 0) ok = wait_or_abort(p_full + 8 * sp, p_phase, abort_p);
       if (td == 0 && i == 3) B200Q_STAMP(6);
-      ok = ok && wait_or_abort(a_empty + 8 * sa, ((i / p.na) & 1) ^ 1, abort_p);
+      ok = ok && wait_or_abort(a_empty + 8 * sa, a_phase, abort_p);
       if (!ok) break;
       if (td == 0 && i < 12) B200Q_STAMP(32 + 2 * i);
-      const uint32_t p_stage = p_ring + sp * PackedStage<FMT>::kBytes;
+      const uint32_t p_stage = p_ring + sp * p_group_bytes + ps * PackedStage<FMT>::kBytes;
       const uint32_t a_stage = a_ring + sa * kStageBytesA;
       if (td == 0 && i == 3) B200Q_STAMP(7);
       if (ATM) {
@@ -488,54 +511,54 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         // The packed stage is read row-wise; the TMA 64-byte swizzle keeps that conflict-free.
         const uint32_t prow = p_stage + (FMT == FMT_W8 ? atm_kh * (kBlockN * 64) : 0) + atm_row * 64;
         const int xr = (atm_row >> 1) & 3;
-        uint32_t out[32];
         // fp16 activations: (1024 + n) - (1024 + zero) is exact, then ONE fp16 multiply by the
         // scale (the format's contract).  bf16 activations: the same in bf16, (128 + n) - (128 +
         // zero) exact, one bf16 multiply by the scale rounded to bf16.
         constexpr bool kBf = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+        const uint32_t a_stage_t = atm_taddr + sa * 64;
+        if (td == 0 && i == 3) B200Q_STAMP(61);
         if (FMT == FMT_W4_REF) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 v = ld_shared_v4(prow + ((c ^ xr) << 4));
-            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              // bytes (b0,b1,b2,b3) -> (b0,b2,b1,b3): the 0x000F000F / 0x00F000F0 masks then
-              // pick (b0,b1) from the word and (b2,b3) from the word shifted by 8
-              const uint32_t u = prmt(words[w], 0u, 0x3120);
-              if (atm_kh == 0) {
-                out[(c * 4 + w) * 2] = deq_lo<kBf>(u, gp);
-                out[(c * 4 + w) * 2 + 1] = deq_lo<kBf>(u >> 8, gp);
-              } else {
-                out[(c * 4 + w) * 2] = deq_hi<kBf>(u, gp);
-                out[(c * 4 + w) * 2 + 1] = deq_hi<kBf>(u >> 8, gp);
-              }
-            }
-          }
-        } else if (FMT == FMT_W4_ASYM) {
+          // This thread unpacks bytes 32*kh .. 32*kh+31 of its row: low nibbles are K offsets
+          // 32*kh + j (columns 16*kh..), high nibbles K offsets 64 + 32*kh + j (columns 32 + 16*kh..).
+          uint32_t lo[16], hi[16];
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             const uint4 v = ld_shared_v4(prow + (((2 * atm_kh + c) ^ xr) << 4));
             const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-              const uint32_t word = words[w];
-              // byte k holds nibbles 2k (low) and 2k+1 (high).  Target halves:
-              //   (n0,n1) = (B0.lo, B0.hi)  (n2,n3) = (B1.lo, B1.hi) ...
-              // (B0.lo, B1.lo) = (n0,n2) and (B0.hi, B1.hi) = (n1,n3) come from one shuffled
-              // word; interleave the two results with a byte permute.
-              const uint32_t u = prmt(word, 0u, 0x3120);            // (B0,B2,B1,B3)
-              const uint32_t lo01 = deq_lo<kBf>(u, gp);        // n0,n2
-              const uint32_t hi01 = deq_hi<kBf>(u, gp);        // n1,n3
-              const uint32_t lo23 = deq_lo<kBf>(u >> 8, gp);   // n4,n6
-              const uint32_t hi23 = deq_hi<kBf>(u >> 8, gp);   // n5,n7
-              out[(c * 4 + w) * 4 + 0] = prmt(lo01, hi01, 0x5410);   // n0,n1
-              out[(c * 4 + w) * 4 + 1] = prmt(lo01, hi01, 0x7632);   // n2,n3
-              out[(c * 4 + w) * 4 + 2] = prmt(lo23, hi23, 0x5410);   // n4,n5
-              out[(c * 4 + w) * 4 + 3] = prmt(lo23, hi23, 0x7632);   // n6,n7
+              // bytes (b0,b1,b2,b3) -> (b0,b2,b1,b3): the masks then pick (b0,b1) from the word
+              // and (b2,b3) from the word shifted by 8
+              const uint32_t u = prmt(words[w], 0u, 0x3120);
+              lo[(c * 4 + w) * 2] = deq_lo<kBf>(u, gp);
+              lo[(c * 4 + w) * 2 + 1] = deq_lo<kBf>(u >> 8, gp);
+              hi[(c * 4 + w) * 2] = deq_hi<kBf>(u, gp);
+              hi[(c * 4 + w) * 2 + 1] = deq_hi<kBf>(u >> 8, gp);
             }
           }
+          tmem_st_x16(a_stage_t + 16 * atm_kh, lo);
+          tmem_st_x16(a_stage_t + 32 + 16 * atm_kh, hi);
+        } else if (FMT == FMT_W4_ASYM) {
+          // words 8*kh .. 8*kh+7 of the row: 64 consecutive K (columns 32*kh..); the layout's
+          // nibble order makes every lop3 pair a pair of K neighbours
+          uint32_t out[32];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const uint4 v = ld_shared_v4(prow + (((2 * atm_kh + c) ^ xr) << 4));
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const uint32_t u = words[w];
+              out[(c * 4 + w) * 4 + 0] = deq_lo<kBf>(u, gp);        // inputs 0,1
+              out[(c * 4 + w) * 4 + 1] = deq_hi<kBf>(u, gp);        // inputs 2,3
+              out[(c * 4 + w) * 4 + 2] = deq_lo<kBf>(u >> 8, gp);   // inputs 4,5
+              out[(c * 4 + w) * 4 + 3] = deq_hi<kBf>(u >> 8, gp);   // inputs 6,7
+            }
+          }
+          tmem_st_x32(a_stage_t + 32 * atm_kh, out);
         } else {
+          // W8: sub-tile kh of the stage holds K offsets 64*kh .. 64*kh+63 of this row
+          uint32_t out[32];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const uint4 v = ld_shared_v4(prow + ((c ^ xr) << 4));
@@ -548,9 +571,8 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               out[(c * 4 + w) * 2 + 1] = pack_operand<T>(k23);
             }
           }
+          tmem_st_x32(a_stage_t + 32 * atm_kh, out);
         }
-        if (td == 0 && i == 3) B200Q_STAMP(61);
-        tmem_st_x32(atm_taddr + sa * 64, out);
         if (td == 0 && i == 3) B200Q_STAMP(62);
         tmem_st_wait();
         if (td == 0 && i == 3) B200Q_STAMP(63);
@@ -619,9 +641,20 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(a_full + 8 * sa);
-        mbar_arrive(p_empty + 8 * sp);
+        if (ps == p.pg - 1 || i == nkb - 1) mbar_arrive(p_empty + 8 * sp);
       }
       if (td == 0 && i < 12) B200Q_STAMP(33 + 2 * i);
+      if (++sa == p.na) {
+        sa = 0;
+        a_phase ^= 1;
+      }
+      if (++ps == p.pg) {
+        ps = 0;
+        if (++sp == p.np) {
+          sp = 0;
+          p_phase ^= 1;
+        }
+      }
     }
     if (!ok) flag_failure(abort_p, p.status, 4u);
 
@@ -653,7 +686,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       // 16-byte row-contiguous stores (the operand rings are idle by now)
       const uint32_t stage = x_ring;
       const bool vec_out = (p.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) &&
-                           (p.nx * x_atom_bytes >= p.tok * 256);
+                           (p.nx * x_chunk_bytes >= p.tok * 256);
       if (acc_ok && nkb > 0) {
         for (int c = 0; c < half_cols; c += 8) {
           uint32_t r[8];
@@ -787,33 +820,34 @@ static EncodeTiledFn encode_fn() {
 
 struct MapKey {
   const void* ptr;
-  uint64_t d0, d1, ld;
-  uint32_t b0, b1, kind;
+  uint64_t d0, d1, d2, ld1, ld2;
+  uint32_t b0, b1, b2, kind;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 &&
-           kind == o.kind;
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && ld1 == o.ld1 && ld2 == o.ld2 &&
+           b0 == o.b0 && b1 == o.b1 && b2 == o.b2 && kind == o.kind;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
-    h ^= (k.d0 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
-    h ^= (k.d1 + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
-    h ^= (k.ld + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
-    h ^= ((static_cast<uint64_t>(k.b0) << 32 | k.b1) + (h << 6) + (h >> 2));
-    h ^= k.kind;
+    auto mix = [&h](uint64_t v) { h ^= (v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2)); };
+    mix(k.d0); mix(k.d1); mix(k.d2); mix(k.ld1); mix(k.ld2);
+    mix((static_cast<uint64_t>(k.b0) << 40) ^ (static_cast<uint64_t>(k.b1) << 20) ^ k.b2);
+    mix(k.kind);
     return static_cast<size_t>(h);
   }
 };
 
-// Tensor maps are pure functions of (pointer, shape, pitch, box): cache them.
-// Encoding is a host-only driver call, legal while a stream is capturing.
-static bool get_tensor_map(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, int elem_bytes,
-                           uint64_t d0, uint64_t d1, uint64_t ld_bytes, uint32_t b0, uint32_t b1,
-                           CUtensorMapSwizzle swz) {
+// Rank-3 tensor maps {d0, d1, d2} with byte pitches {ld1, ld2} and box {b0, b1, b2}.  They are
+// pure functions of their arguments: cached.  Encoding is a host-only driver call, legal while
+// a stream is capturing.
+static bool get_tensor_map(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint64_t d0,
+                           uint64_t d1, uint64_t d2, uint64_t ld1, uint64_t ld2, uint32_t b0,
+                           uint32_t b1, uint32_t b2, CUtensorMapSwizzle swz) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  MapKey key{ptr, d0, d1, ld_bytes, b0, b1, static_cast<uint32_t>(dt) * 16u + static_cast<uint32_t>(swz)};
+  MapKey key{ptr, d0, d1, d2, ld1, ld2, b0, b1, b2,
+             static_cast<uint32_t>(dt) * 16u + static_cast<uint32_t>(swz)};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -827,16 +861,17 @@ static bool get_tensor_map(CUtensorMap* out, const void* ptr, CUtensorMapDataTyp
     set_last_error_text("cuTensorMapEncodeTiled entry point not found");
     return false;
   }
-  cuuint64_t dims[2] = {d0, d1};
-  cuuint64_t strides[1] = {ld_bytes};
-  cuuint32_t box[2] = {b0, b1};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {ld1, ld2};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  (void)elem_bytes;
   if (r != CUDA_SUCCESS) {
-    set_last_error_text("cuTensorMapEncodeTiled failed");
+    char text[160];
+    std::snprintf(text, sizeof(text), "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    set_last_error_text(text);
     return false;
   }
   std::lock_guard<std::mutex> g(mu);
@@ -852,7 +887,7 @@ constexpr size_t kWsHeaderBytes = 64 * 1024;
 constexpr int kMaxSplitTiles = static_cast<int>((kWsHeaderBytes - 256) / sizeof(unsigned));
 
 struct TcPlan {
-  int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, tmem_cols, a_col0;
+  int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, pg, xg, tmem_cols, a_col0;
   bool atm;          // A operand in tensor memory (default) or in shared memory
   size_t smem_bytes;
 };
@@ -880,12 +915,17 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   pl.n_tiles = (N + kBlockN - 1) / kBlockN;
   pl.kb_total = (K + kBlockK - 1) / kBlockK;
 
+  // Rings.  One TMA instruction fills a weight GROUP of `pg` K blocks and another an
+  // activation CHUNK of `xg` K blocks, so that the single producer thread and the single MMA
+  // thread touch a barrier once per group/chunk instead of once per block.
   const int pbytes = packed_stage_bytes(format);
-  const int xbytes = tok * 128;                    // one activation atom
+  const int xbytes = tok * 256;                    // activations of one K block (two atoms)
   const size_t a_stage_smem = pl.atm ? 0 : kStageBytesA;
+  pl.xg = tok <= 16 ? 4 : (tok <= 32 ? 2 : 1);
+  pl.pg = tok <= 64 ? 2 : 1;
   auto total = [&](int np, int na, int nx) {
-    return static_cast<size_t>(na) * a_stage_smem + static_cast<size_t>(nx) * xbytes +
-           static_cast<size_t>(np) * pbytes + 1024 /*alignment*/ + 8 * kMaxRing * 6 + 64;
+    return static_cast<size_t>(na) * a_stage_smem + static_cast<size_t>(nx) * pl.xg * xbytes +
+           static_cast<size_t>(np) * pl.pg * pbytes + 1024 /*alignment*/ + 8 * kMaxRing * 6 + 64;
   };
   const size_t half_sm = 115712;                   // (228 KiB - 2 x 1 KiB reserved) / 2
   const size_t budget = static_cast<size_t>(kSmemBudget);
@@ -898,19 +938,17 @@ static TcPlan make_plan(int format, int M, int N, int K) {
     // Two resident blocks need <= 256 columns each: narrow tiles (decode, HBM-bound) take
     // that shape so one block's set-up and epilogue overlap the other's weight stream.
     pl.a_col0 = (tok + 63) / 64 * 64;
-    two_per_sm = tok <= 64 && total(4, 0, 4) <= half_sm;
+    two_per_sm = tok <= 64 && total(2, 0, 2) <= half_sm;
     if (two_per_sm) {
       pl.na = (256 - pl.a_col0) / 64;              // 3 for tok <= 64
-      pl.nx = 4;
-      pl.np = 4;
-      while (pl.np < kMaxRing && total(pl.np + 1, 0, pl.nx) <= half_sm) ++pl.np;
+      pl.nx = 3;
+      while (total(pl.np, 0, pl.nx) > half_sm && pl.nx > 2) --pl.nx;
+      while (pl.np < 6 && total(pl.np + 1, 0, pl.nx) <= half_sm) ++pl.np;
       pl.tmem_cols = 256;
     } else {
       pl.na = (512 - pl.a_col0) / 64;
       if (pl.na > 4) pl.na = 4;
-      pl.nx = 4;
-      pl.np = 3;
-      const int wish[][2] = {{1, 6}, {2, 4}, {2, 6}, {1, 8}, {2, 8}};
+      const int wish[][2] = {{1, 3}, {2, 3}, {2, 4}, {1, 4}, {2, 6}, {2, 8}};
       for (const auto& w : wish) {
         int nx = pl.nx, np = pl.np;
         (w[0] == 1 ? nx : np) = w[1];
@@ -919,7 +957,6 @@ static TcPlan make_plan(int format, int M, int N, int K) {
           pl.np = np;
         }
       }
-      while (total(pl.np, 0, pl.nx) > budget && pl.nx > 2) --pl.nx;
       pl.tmem_cols = 512;
     }
   } else {
@@ -927,14 +964,11 @@ static TcPlan make_plan(int format, int M, int N, int K) {
     while (cols < tok) cols <<= 1;
     pl.tmem_cols = cols;
     pl.a_col0 = 0;
-    two_per_sm = tok <= 32 && total(2, 2, 4) <= half_sm;
+    two_per_sm = tok <= 32 && total(2, 2, 2) <= half_sm;
     if (two_per_sm) {
-      pl.nx = 4;
-      while (pl.np < kMaxRing && total(pl.np + 1, pl.na, pl.nx) <= half_sm) ++pl.np;
+      while (pl.np < 4 && total(pl.np + 1, pl.na, pl.nx) <= half_sm) ++pl.np;
     } else {
-      // {ring, depth} wishes in priority order: activations must cover their load latency
-      // first (four atoms), then a third A stage decouples dequantisation from the MMA
-      const int wish[][2] = {{1, 4}, {0, 3}, {2, 3}, {2, 4}, {1, 6}, {2, 6}, {0, 4}, {1, 8}, {2, 8}};
+      const int wish[][2] = {{0, 3}, {2, 3}, {1, 3}, {2, 4}, {0, 4}, {2, 6}};
       for (const auto& w : wish) {
         int na = pl.na, nx = pl.nx, np = pl.np;
         (w[0] == 0 ? na : (w[0] == 1 ? nx : np)) = w[1];
@@ -948,25 +982,35 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   }
   pl.smem_bytes = total(pl.np, pl.na, pl.nx);
 
-  // split-K: choose the smallest split count that fills the resident slots well
+  // split-K: choose the smallest split count that fills the resident slots well.  Wide token
+  // tiles pay for a split with tok x 128 fp32 partials per block written and re-read, so they
+  // split only when less than half of the GPU would otherwise have work, and never into a
+  // second wave.
   const int tiles = pl.m_tiles * pl.n_tiles;
   const int slots = 148 * (two_per_sm ? 2 : 1);
   int max_splits = pl.kb_total / 4;          // at least four K blocks per split
   if (max_splits > 16) max_splits = 16;
   if (max_splits < 1) max_splits = 1;
   int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= max_splits; ++s) {
-    const int ctas = tiles * s;
-    const int waves = (ctas + slots - 1) / slots;
-    const double eff = static_cast<double>(ctas) / (static_cast<double>(waves) * slots);
-    if (eff > best_eff + 0.05) {
-      best_eff = eff;
-      best = s;
+  if (tok > 64) {
+    if (2 * tiles <= slots) {
+      best = slots / tiles;
+      if (best > max_splits) best = max_splits;
     }
-    if (eff >= 0.9) break;
+  } else {
+    double best_eff = 0.0;
+    for (int s = 1; s <= max_splits; ++s) {
+      const int ctas = tiles * s;
+      const int waves = (ctas + slots - 1) / slots;
+      const double eff = static_cast<double>(ctas) / (static_cast<double>(waves) * slots);
+      if (eff > best_eff + 0.05) {
+        best_eff = eff;
+        best = s;
+      }
+      if (eff >= 0.9) break;
+    }
   }
-  if (tiles >= slots || tiles > kMaxSplitTiles) best = 1;
+  if (tiles >= slots || tiles > kMaxSplitTiles || best < 1) best = 1;
   pl.kb_per_split = (pl.kb_total + best - 1) / best;
   pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
   return pl;
@@ -982,7 +1026,8 @@ size_t tc_workspace_bytes(int format, int M, int N, int K) {
 
 bool tc_supported(const ForwardArgs& a) {
   if (a.format != FMT_W8 && a.group != 128) return false;
-  if (a.format == FMT_W8 ? (a.K % 16 != 0) : (a.K % 128 != 0)) return false;
+  // K must be whole 64-element atoms (the tensor maps' third dimension walks them)
+  if (a.format == FMT_W8 ? (a.K % 64 != 0) : (a.K % 128 != 0)) return false;
   if (reinterpret_cast<uintptr_t>(a.x) % 16 || (a.ldx * 2) % 16) return false;
   if (reinterpret_cast<uintptr_t>(a.w) % 16 || a.ldw % 16) return false;
   return true;
@@ -1008,17 +1053,21 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
     }
   }
   CUtensorMap tm_w, tm_x;
-  const uint64_t w_cols = (FMT == FMT_W8) ? static_cast<uint64_t>(a.K) : static_cast<uint64_t>(a.K / 2);
-  // the A-in-TMEM variant reads the packed stage one row per thread: 64-byte swizzle
-  if (!get_tensor_map(&tm_w, a.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_cols, static_cast<uint64_t>(a.N),
-                      static_cast<uint64_t>(a.ldw), 64, kBlockN,
+  // Packed weights as {64 B, N rows, K chunks of 64 B}: the third coordinate walks K, so a
+  // box of depth pg (2 pg for int8, whose K block is two 64-byte chunks) is a weight group.
+  // The A-in-TMEM variant reads a stage one row per thread: 64-byte swizzle.
+  const uint64_t w_row_bytes = (FMT == FMT_W8) ? static_cast<uint64_t>(a.K) : static_cast<uint64_t>(a.K / 2);
+  if (!get_tensor_map(&tm_w, a.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 64, static_cast<uint64_t>(a.N),
+                      w_row_bytes / 64, static_cast<uint64_t>(a.ldw), 64, 64, kBlockN,
+                      static_cast<uint32_t>((FMT == FMT_W8 ? 2 : 1) * pl.pg),
                       ATM ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE))
     return B200Q_ERR_CUDA;
+  // Activations as {64 elements, M rows, K atoms}: a box of depth 2 xg is an activation chunk.
   const CUtensorMapDataType xdt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if (!get_tensor_map(&tm_x, a.x, xdt, 2, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
-                      static_cast<uint64_t>(a.ldx) * 2, 64, static_cast<uint32_t>(pl.tok),
-                      CU_TENSOR_MAP_SWIZZLE_128B))
+  if (!get_tensor_map(&tm_x, a.x, xdt, 64, static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.K / 64),
+                      static_cast<uint64_t>(a.ldx) * 2, 128, 64, static_cast<uint32_t>(pl.tok),
+                      static_cast<uint32_t>(2 * pl.xg), CU_TENSOR_MAP_SWIZZLE_128B))
     return B200Q_ERR_CUDA;
 
   TcParams p{};
@@ -1042,6 +1091,8 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.np = pl.np;
   p.na = pl.na;
   p.nx = pl.nx;
+  p.pg = pl.pg;
+  p.xg = pl.xg;
   p.static_weights = a.static_weights ? 1 : 0;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   p.status = reinterpret_cast<unsigned*>(ws);

@@ -145,7 +145,9 @@ __global__ void __launch_bounds__(256) quantize_w4_kernel(const T* __restrict__ 
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float v = clamp_nan0(rintf(__fdiv_rn(load_as_float(row, k0 + i), s)) + zp, 0.0f, 15.0f);
-        word |= static_cast<uint32_t>(static_cast<int>(v)) << (4 * i);
+        // input i of the word sits at nibble position (i & 1) * 4 + (i >> 1): positions
+        // 0..7 hold inputs 0,2,4,6,1,3,5,7
+        word |= static_cast<uint32_t>(static_cast<int>(v)) << (4 * ((i & 1) * 4 + (i >> 1)));
       }
       prow[idx] = word;
     }

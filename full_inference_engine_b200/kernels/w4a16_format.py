@@ -8,7 +8,7 @@ purpose — it is the arithmetic ``reference_mode`` compares the kernels with.
 Reference layout ("split-half"): group of G inputs -> G/2 bytes, byte j = input j (low
 nibble) | input j+G/2 (high nibble), values in [-7,7] stored +8, one fp16 scale per
 (row, group).  A second, asymmetric layout (fp16 scale and zero-point, eight nibbles per
-int32 in K order) is this library's own: ``quantize_weight_w4_asym``.
+int32, pairs of K-neighbours 16 bits apart) is this library's own: ``quantize_weight_w4_asym``.
 """
 
 from __future__ import annotations
@@ -68,7 +68,8 @@ def quantize_weight_w4_asym(weight: torch.Tensor, group_size: int = GROUP_SIZE,
 
     Asymmetric 4-bit (no counterpart in the reference): per group ``lo=min(min w,0)``,
     ``hi=max(max w,0)``, ``s=max((hi-lo)/15,1e-8)``, ``zp=clamp(round(-lo/s),0,15)``,
-    ``q=clamp(round(w/s)+zp,0,15)``; nibble ``i`` of word ``j`` is input ``8j+i``.
+    ``q=clamp(round(w/s)+zp,0,15)``; word ``j`` holds inputs ``8j..8j+7`` with input ``i`` at
+    nibble position ``(i & 1) * 4 + (i >> 1)``.
     """
     n, k = _check_weight(weight, group_size, 8)
     w = _as_kernel_input(weight)
@@ -107,7 +108,8 @@ def unpack_w4_asym_reference(packed: torch.Tensor, scales: torch.Tensor, zeros: 
     if packed.dtype is not torch.int32:
         raise ValueError("packed weights must be int32")
     rows = packed.shape[0]
-    shifts = 4 * torch.arange(8, dtype=torch.int32, device=packed.device)
+    positions = [(i & 1) * 4 + (i >> 1) for i in range(8)]      # where input i sits in its word
+    shifts = 4 * torch.tensor(positions, dtype=torch.int32, device=packed.device)
     nibbles = (packed.reshape(rows, in_features // 8, 1) >> shifts) & 0xF
     q = nibbles.reshape(rows, in_features // group_size, group_size).to(torch.float16)
     centred = q - zeros.to(torch.float16)[..., None]

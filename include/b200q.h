@@ -46,8 +46,11 @@ typedef enum b200q_w4_layout {
    * byte j of a group holds input j (low nibble) and input j+G/2 (high
    * nibble).  packed [N, K/2] uint8, scales [N, K/G] fp16, no zero-points. */
   B200Q_W4_REF_SPLIT_HALF_SYM = 0,
-  /* Asymmetric 4-bit, eight nibbles per int32 in K order (nibble i of word w
-   * is input 8w+i), fp16 scale and fp16 zero-point per group.
+  /* Asymmetric 4-bit, eight nibbles per int32, fp16 scale and fp16 zero-point
+   * per group.  Word w holds inputs 8w..8w+7; nibble position p (bits 4p..4p+3)
+   * holds input 8w + {0,2,4,6,1,3,5,7}[p], i.e. input i sits at position
+   * (i & 1) * 4 + (i >> 1): the two nibbles 16 bits apart are neighbours in K,
+   * which is what a half2 unpack wants.
    * packed [N, K/8] int32, scales [N, K/G] fp16, zeros [N, K/G] fp16.
    * The reference has no such layout; its definition is this library's.    */
   B200Q_W4_ASYM_ZP_INT32 = 1

@@ -70,7 +70,8 @@ def unpack_w4_asym(packed: torch.Tensor, scales: torch.Tensor, zeros: torch.Tens
                    in_features: int, group_size: int = 128) -> torch.Tensor:
     """Dequantise the asymmetric int32 layout (no reference counterpart) to fp16."""
     n = packed.shape[0]
-    shifts = 4 * torch.arange(8, dtype=torch.int32)
+    # input i of a word sits at nibble position (i & 1) * 4 + (i >> 1)
+    shifts = 4 * torch.tensor([(i & 1) * 4 + (i >> 1) for i in range(8)], dtype=torch.int32)
     nibbles = (packed.reshape(n, in_features // 8, 1) >> shifts) & 0xF
     q = nibbles.reshape(n, in_features // group_size, group_size).to(torch.float32)
     centred = (q - zeros.float()[..., None]).to(torch.float16)

@@ -106,12 +106,17 @@ def weight_bytes(in_features: int, out_features: int, group_size: int = GROUP_SI
 
 
 # --------------------------------------------------------------------------- W4 asymmetric (no reference)
+# nibble position of input i inside its int32 word
+ASYM_POSITION = np.array([(i & 1) * 4 + (i >> 1) for i in range(8)])
+
+
 def quantize_w4_asym(weight: np.ndarray, group_size: int = GROUP_SIZE):
     """Asymmetric 4-bit, fp16 scale + fp16 zero-point per group, 8 nibbles per int32.
 
     PARITY UNPINNED: the reference defines no such layout.  Per (row, group):
     lo=min(min w,0), hi=max(max w,0), s=max((hi-lo)/15,1e-8), zp=clip(rint(-lo/s),0,15),
-    q=clip(rint(w/s)+zp,0,15); word[n,k//8] = sum_i q[n,8*(k//8)+i] << 4i.
+    q=clip(rint(w/s)+zp,0,15); input i of a word sits at nibble position
+    ``(i & 1) * 4 + (i >> 1)`` (positions 0..7 hold inputs 0,2,4,6,1,3,5,7).
     """
     if weight.ndim != 2:
         raise ValueError("weight must be [out_features, in_features]")
@@ -126,7 +131,7 @@ def quantize_w4_asym(weight: np.ndarray, group_size: int = GROUP_SIZE):
     zp = np.clip(np.rint(-lo / s), 0.0, 15.0).astype(np.float32)
     q = np.clip(np.rint(v / s[..., None]) + zp[..., None], 0.0, 15.0).astype(np.uint32)
     q = q.reshape(n, k // 8, 8)
-    shifts = (4 * np.arange(8, dtype=np.uint32))[None, None, :]
+    shifts = (4 * ASYM_POSITION.astype(np.uint32))[None, None, :]
     words = np.bitwise_or.reduce(q << shifts, axis=-1).astype(np.uint32)
     return (np.ascontiguousarray(words.view(np.int32)), s.astype(np.float16), zp.astype(np.float16))
 
@@ -136,7 +141,7 @@ def unpack_w4_asym(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, in
     """fp16 [N,K]: fp16(nibble - zero) * fp16(scale), product in fp16."""
     n = packed.shape[0]
     words = packed.view(np.uint32).reshape(n, in_features // 8, 1)
-    shifts = (4 * np.arange(8, dtype=np.uint32))[None, None, :]
+    shifts = (4 * ASYM_POSITION.astype(np.uint32))[None, None, :]
     q = ((words >> shifts) & 0xF).reshape(n, in_features // group_size, group_size)
     centred = (q.astype(np.float32) - zeros.astype(np.float32)[..., None]).astype(np.float16)
     return (centred * scales.astype(np.float16)[..., None]).reshape(n, in_features)

@@ -143,12 +143,14 @@ def test_asym_layout_roundtrip_and_nibble_order():
     deq = oracle.unpack_w4_asym(packed, scales, zeros, 256, 128).astype(np.float32)
     err = np.abs(deq - w).reshape(8, 2, 128).max(axis=-1)
     assert np.all(err <= scales.astype(np.float32) / 2 * 1.01 + 1e-4)
-    # nibble i of word j is input 8j+i: one-hot check
+    # input i of word j sits at nibble position (i & 1) * 4 + (i >> 1): one-hot check
     w = np.zeros((1, 128), np.float32)
     w[0, 9] = 1.5       # positive only -> lo = 0, zp = 0, scale = 0.1, q = 15
     packed, scales, zeros = oracle.quantize_w4_asym(w, 128)
     assert float(zeros[0, 0]) == 0.0
-    assert (int(packed.view(np.uint32)[0, 1]) >> 4) & 0xF == 15
+    assert int(packed.view(np.uint32)[0, 1]) == 15 << 16          # input 1 of word 1 -> position 4
+    w[0, 9], w[0, 14] = 0.0, 1.5                                   # input 6 -> position 3
+    assert int(oracle.quantize_w4_asym(w, 128)[0].view(np.uint32)[0, 1]) == 15 << 12
     t = torch.from_numpy
     assert torch.equal(cpu_path.unpack_w4_asym(t(packed), t(scales), t(zeros), 128),
                        t(oracle.unpack_w4_asym(packed, scales, zeros, 128)))
