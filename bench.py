@@ -88,6 +88,12 @@ def build_cases(workload: str, layout: str) -> list[Case]:
                 for name in ("q", "kv", "o", "gate_up", "down") for m in (1, 16, 64, 512)]
     if workload == "c1":
         return [Case("gate_0p6b", "w8", 8, 1024, 3072, torch.float16)]
+    if workload == "c3":
+        # one mixed step of a Qwen3-0.6B-shaped model: 16 decode rows + one 128-token chunk
+        shapes = {"q": (1024, 2048), "k": (1024, 1024), "v": (1024, 1024), "o": (2048, 1024),
+                  "gate": (1024, 3072), "up": (1024, 3072), "down": (3072, 1024)}
+        return [Case(f"L{layer:02d}.{name}", "w8", 144, k, n, torch.float16)
+                for layer in range(28) for name, (k, n) in shapes.items()]
     raise SystemExit(f"unknown workload {workload}")
 
 
@@ -327,7 +333,9 @@ def config_dict(args, cases, rotation):
                      "c5": "config 5: INT4 g128 prefill M=4096 bf16 with 1% outlier rows, "
                            "gate/up and down",
                      "c4": "config 4: W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, M in {1,16,64,512}",
-                     "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16"}[args.workload],
+                     "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16",
+                     "c3": "config 3: 28 x 7 random-init Qwen3-0.6B W8A16 projections, one mixed "
+                           "step of M=144 rows (16 decode + 128 prefill), fp16, one CUDA graph"}[args.workload],
         "layout": {"asym": "asymmetric int32 x8 nibbles + fp16 scale and zero-point",
                    "ref": "reference split-half uint8 + fp16 scale"}[args.layout]
         if cases[0].fmt != "w8" else "int8 per-channel fp16 scale",
@@ -359,7 +367,7 @@ def run_b200(args, cases):
             print(f"# rank {rank}: {msg}", file=sys.stderr, flush=True)
 
     pk = peaks()
-    copies = 10 if args.workload in ("c2", "c1") else (4 if args.workload == "c4" else 3)
+    copies = {"c1": 48, "c2": 10, "c3": 1, "c4": 4, "c5": 6}[args.workload]
     weight_sets = make_weight_sets(cases, copies, device, rank, world)
     acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
     # per-rank view of each case
@@ -367,25 +375,30 @@ def run_b200(args, cases):
     gathered = [torch.empty(world, c.m, c.n // world, dtype=c.dtype, device=device) if world > 1 else None
                 for c in cases]
 
-    def one_step(variant: int):
+    def one_step(variant: int, gather: bool = True):
         outs = []
         for i, case in enumerate(local_cases):
             sets = weight_sets[(case.fmt, case.name)]
             w = sets[(i + variant * len(local_cases)) % len(sets)]
             y = forward(case, acts[i], w)
-            if world > 1:
+            if world > 1 and gather:
                 dist.all_gather_into_tensor(gathered[i], y)
             outs.append(y)
         return outs
 
     step_weight_bytes = sum(c.weight_bytes() for c in local_cases)
-    rotation = (f"inputs larger than L2: each case reads its own weight buffer and two step "
-                f"variants alternate, {2 * step_weight_bytes / 2**20:.0f} MiB of distinct weights "
-                f"between reuses (L2 = 126 MiB)")
+    # enough step variants (each on its own weight copies) that >= 2 x L2 of distinct weights
+    # pass between two uses of the same buffer
+    variants = max(1, min(copies, -(-2 * L2_BYTES // step_weight_bytes)))
+    if copies > 1:
+        variants = max(2, variants)
+    rotation = (f"inputs larger than L2: each case reads its own weight buffer and {variants} step "
+                f"variant(s) alternate, {variants * step_weight_bytes / 2**20:.0f} MiB of distinct "
+                f"weights between reuses (L2 = 126 MiB)")
 
     # eager warm-up (also sizes the workspace), then capture two step variants
     note("inputs ready")
-    for v in (0, 1):
+    for v in range(variants):
         one_step(v)
     torch.cuda.synchronize()
     note("eager warm-up done")
@@ -407,7 +420,7 @@ def run_b200(args, cases):
         return float(host_y[-1][0, 0])
 
     for j in range(3):
-        e2e_step(j & 1)
+        e2e_step(j % variants)
     if world > 1:
         dist.barrier()
     e2e_steps = max(3, min(args.steps, 50))
@@ -415,7 +428,7 @@ def run_b200(args, cases):
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     for j in range(e2e_steps):
-        e2e_step(j & 1)
+        e2e_step(j % variants)
     e.record()
     torch.cuda.synchronize()
     e2e_ms = max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / e2e_steps
@@ -430,7 +443,7 @@ def run_b200(args, cases):
     graphs = []
     use_graph = True
     try:
-        for v in (0, 1):
+        for v in range(variants):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 one_step(v)
@@ -441,14 +454,14 @@ def run_b200(args, cases):
         torch.cuda.synchronize()
         if rank == 0:
             print(f"# graph capture failed ({exc}); timing eager launches", file=sys.stderr)
-    launches_per_step = (_lib.launch_count() - launches_before) // 2 if use_graph else len(cases)
+    launches_per_step = (_lib.launch_count() - launches_before) // variants if use_graph else len(cases)
     note(f"capture done (graph={use_graph})")
 
     def run_step(i):
         if use_graph:
-            graphs[i & 1].replay()
+            graphs[i % variants].replay()
         else:
-            one_step(i & 1)
+            one_step(i % variants)
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -482,11 +495,45 @@ def run_b200(args, cases):
     ms_step = ms_total / args.steps
     note(f"timed region done: {ms_step:.4f} ms/step")
 
+    # ---- multi-rank only: the sharded GEMMs alone (no collective), same protocol, so the
+    # line can show how the compute phase and the gather phase each scale
+    gemm_only_ms = None
+    if world > 1:
+        torch.cuda.synchronize()
+        for v in range(variants):
+            one_step(v, gather=False)
+        solo = []
+        for v in range(variants):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                one_step(v, gather=False)
+            solo.append(g)
+        for j in range(16):
+            solo[j % variants].replay()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for j in range(args.steps):
+            solo[j % variants].replay()
+        s1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s0.elapsed_time(s1) / args.steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gemm_only_ms = float(t.item())
+        note(f"gemm-only: {gemm_only_ms:.4f} ms/step")
+
     # ---- per-case latency (roofline): R back-to-back launches over rotating weight copies
     per_case = []
     # per-case latencies are a single-GPU diagnostic; the multi-rank run reports the step only
     for i, case in enumerate(local_cases if world == 1 else []):
-        sets = weight_sets[(case.fmt, case.name)]
+        if args.workload == "c3":
+            if not case.name.startswith("L00."):
+                continue
+            # the same projection of all 28 layers: 28 distinct weight buffers in rotation
+            suffix = case.name.split(".", 1)[1]
+            sets = [weight_sets[(c.fmt, c.name)][0] for c in local_cases if c.name.endswith("." + suffix)]
+        else:
+            sets = weight_sets[(case.fmt, case.name)]
         reps = len(sets)
         for w in sets[:2]:
             forward(case, acts[i], w)
@@ -523,7 +570,7 @@ def run_b200(args, cases):
         total_bytes = sum(c.bytes for c in cases)          # whole job, all ranks
         total_flops = sum(c.flops for c in cases)
         dominant = max(per_case, key=lambda r: r["us"]) if per_case else None
-        step_us = sum(r["us"] for r in per_case)
+        step_us = sum(r["us"] for r in per_case) * (28 if args.workload == "c3" else 1)
         line = {
             "metric": METRIC, "value": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "unit": "GB/s",
             "tflops": round(total_flops / (ms_step * 1e-3) / 1e12, 3),
@@ -544,6 +591,9 @@ def run_b200(args, cases):
                             "from pinned host memory and results return to it every step"},
             "gpu_launches": int(launches_per_step * args.steps),
             "timing": "cuda-graph replay" if use_graph else "eager launches",
+            "phases": None if gemm_only_ms is None else {
+                "sharded_gemm_only_ms_per_step": round(gemm_only_ms, 5),
+                "with_all_gather_ms_per_step": round(ms_step, 5)},
             "device_status": status,
         }
         if world == 1:
@@ -585,7 +635,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")

@@ -27,10 +27,14 @@ int note_launch() {
   return B200Q_OK;
 }
 
-// Rows of decode width go to the CUDA-core kernel: it needs no workspace, no
-// tensor maps and no TMEM, and at M <= 2 its arithmetic fits under the weight
-// stream.  Everything wider is a contraction and belongs on the tensor cores.
-constexpr int kSimtMaxRows = 2;
+// The tensor-core kernel serves every M it supports: even at M = 1 the dequantisation, not the
+// multiply, is what costs instructions, and handing the multiply-accumulate to the (otherwise
+// idle) tensor cores leaves the CUDA cores half the work of the all-CUDA-core kernel.  The
+// CUDA-core split-K kernel remains for geometries the tensor-core kernel does not take (group
+// sizes other than 128, K not a multiple of 64), on request (B200Q_KERNEL_SIMT), and for a
+// single int8 row, where there is hardly any unpacking and it measured faster.
+constexpr int kSimtMaxRowsW4 = 0;
+constexpr int kSimtMaxRowsW8 = 1;
 
 static int run_forward(ForwardArgs& a, int kernel_and_flags) {
   a.static_weights = (kernel_and_flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
@@ -38,7 +42,8 @@ static int run_forward(ForwardArgs& a, int kernel_and_flags) {
   if (kernel == B200Q_KERNEL_SIMT) return launch_forward_simt(a);
   if (kernel == B200Q_KERNEL_TC) return launch_forward_tc(a);
   if (kernel != B200Q_KERNEL_AUTO) return B200Q_ERR_INVALID;
-  if (a.M <= kSimtMaxRows || !tc_supported(a)) return launch_forward_simt(a);
+  const int simt_rows = a.format == FMT_W8 ? kSimtMaxRowsW8 : kSimtMaxRowsW4;
+  if (a.M <= simt_rows || !tc_supported(a)) return launch_forward_simt(a);
   return launch_forward_tc(a);
 }
 

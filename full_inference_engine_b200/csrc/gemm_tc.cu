@@ -755,25 +755,60 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
       if (*last_p) {
         __threadfence();
-        if (n < p.N) {
-          for (int c = 0; c < half_cols; c += 8) {
-            float v[8];
+        // Sum the partials of this tile in split order.  Flat mapping: a row of the tile is
+        // 128 channels = 32 float4; 8 rows per pass and 4 passes in flight per thread keep
+        // 4 x splits independent 16-byte loads outstanding (the partials sit in L2).
+        const int n_base = n_tile * kBlockN;
+        const int q4 = td & 31;                           // float4 index inside the row
+        const int nq = n_base + 4 * q4;
+        const int rows = min(p.tok, p.M - m_base);
+        const bool vec4 = (p.N % 4 == 0) && (nq + 4 <= p.N);
+        float sc[4] = {1.0f, 1.0f, 1.0f, 1.0f}, bs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-            for (int z = 0; z < p.splits; ++z) {
-              float t[8];
+        for (int e = 0; e < 4; ++e) {
+          if (nq + e < p.N) {
+            if (FMT == FMT_W8)
+              sc[e] = p.scale_is_f32 ? reinterpret_cast<const float*>(p.scales)[nq + e]
+                                     : __half2float(reinterpret_cast<const __half*>(p.scales)[nq + e]);
+            if (p.bias != nullptr) bs[e] = static_cast<float>(static_cast<const T*>(p.bias)[nq + e]);
+          }
+        }
+        for (int r0 = td >> 5; r0 < rows; r0 += 32) {
+          float4 acc[4];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int m = min(m_base + c_begin + c + j, p.M - 1);
-                t[j] = __ldcg(p.partial + (static_cast<int64_t>(z) * p.M + m) * p.N + n);
+          for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          for (int z = 0; z < p.splits; ++z) {
+            float4 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int r = min(r0 + 8 * u, rows - 1);
+              const float* src = p.partial + (static_cast<int64_t>(z) * p.M + m_base + r) * p.N + nq;
+              if (vec4) {
+                t[u] = __ldcg(reinterpret_cast<const float4*>(src));
+              } else {
+                t[u].x = (nq + 0 < p.N) ? __ldcg(src + 0) : 0.0f;
+                t[u].y = (nq + 1 < p.N) ? __ldcg(src + 1) : 0.0f;
+                t[u].z = (nq + 2 < p.N) ? __ldcg(src + 2) : 0.0f;
+                t[u].w = (nq + 3 < p.N) ? __ldcg(src + 3) : 0.0f;
               }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] += t[j];
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int m = m_base + c_begin + c + j;
-              if (m < p.M) yT[static_cast<int64_t>(m) * p.ldy + n] = from_float<T>(v[j] * ch_scale + ch_bias);
+            for (int u = 0; u < 4; ++u) {
+              acc[u].x += t[u].x;
+              acc[u].y += t[u].y;
+              acc[u].z += t[u].z;
+              acc[u].w += t[u].w;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int r = r0 + 8 * u;
+            if (r < rows) {
+              T* dst = yT + static_cast<int64_t>(m_base + r) * p.ldy + nq;
+              const float v[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (nq + e < p.N) dst[e] = from_float<T>(v[e] * sc[e] + bs[e]);
             }
           }
         }
@@ -995,6 +1030,8 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   if (tok > 64) {
     if (2 * tiles <= slots) {
       best = slots / tiles;
+      const int cap = pl.kb_total / 8;         // a wide tile's split must be worth its reduction
+      if (best > cap) best = cap;
       if (best > max_splits) best = max_splits;
     }
   } else {
