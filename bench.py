@@ -359,8 +359,24 @@ def run_b200(args, cases):
             raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    cpu_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+        # barriers and the max-over-ranks of the timings go over a gloo side group, so that
+        # the only NCCL work in the run is the all-gather being measured
+        cpu_group = dist.new_group(backend="gloo")
+
+    def max_over_ranks(value: float) -> float:
+        if world == 1:
+            return value
+        t = torch.tensor([value], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=cpu_group)
+        return float(t.item())
+
+    def barrier():
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=cpu_group)
 
     def note(msg):
         if args.verbose:
@@ -421,8 +437,7 @@ def run_b200(args, cases):
 
     for j in range(3):
         e2e_step(j % variants)
-    if world > 1:
-        dist.barrier()
+    barrier()
     e2e_steps = max(3, min(args.steps, 50))
     t0 = time.perf_counter()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -431,11 +446,7 @@ def run_b200(args, cases):
         e2e_step(j % variants)
     e.record()
     torch.cuda.synchronize()
-    e2e_ms = max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / e2e_steps)
 
     note(f"e2e done: {e2e_ms:.4f} ms/step")
 
@@ -475,23 +486,15 @@ def run_b200(args, cases):
         run_step(j)
     torch.cuda.synchronize()
     note("warm-up replays done")
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
+    barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for j in range(args.steps):
         run_step(j)
     end.record()
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-    ms_total = start.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([ms_total], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    barrier()
+    ms_total = max_over_ranks(start.elapsed_time(end))
     ms_step = ms_total / args.steps
     note(f"timed region done: {ms_step:.4f} ms/step")
 
@@ -517,9 +520,7 @@ def run_b200(args, cases):
             solo[j % variants].replay()
         s1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([s0.elapsed_time(s1) / args.steps], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        gemm_only_ms = float(t.item())
+        gemm_only_ms = max_over_ranks(s0.elapsed_time(s1) / args.steps)
         note(f"gemm-only: {gemm_only_ms:.4f} ms/step")
 
     # ---- per-case latency (roofline): R back-to-back launches over rotating weight copies
