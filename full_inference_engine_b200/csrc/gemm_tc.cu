@@ -35,9 +35,7 @@
 
 namespace b200q {
 
-constexpr int kTcThreads = 320;
-constexpr int kDequantThreads = 256;
-constexpr int kDequantWarps = 8;
+// Block = 2 service warps (TMA producer, MMA issuer) + DW dequantise warps (8 or 16).
 constexpr int kBlockN = 128;                 // output channels per block (UMMA M)
 constexpr int kBlockK = 128;                 // K elements per pipeline step
 constexpr int kAtomBytesA = kBlockN * 128;   // one 64-wide K atom of the A operand: 16 KB
@@ -236,8 +234,24 @@ __device__ __forceinline__ void load_group_chunk(GroupChunk& g, const TcParams& 
   }
 }
 
-template <int FMT, typename T, bool ATM>
-__global__ void __launch_bounds__(kTcThreads, ATM ? 2 : 1)
+// Column-count generic TMEM store of one thread's lane.
+template <int NCOL>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[NCOL]);
+template <>
+__device__ __forceinline__ void tmem_st_cols<8>(uint32_t taddr, const uint32_t (&r)[8]) {
+  tmem_st_x8(taddr, r);
+}
+template <>
+__device__ __forceinline__ void tmem_st_cols<16>(uint32_t taddr, const uint32_t (&r)[16]) {
+  tmem_st_x16(taddr, r);
+}
+template <>
+__device__ __forceinline__ void tmem_st_cols<32>(uint32_t taddr, const uint32_t (&r)[32]) {
+  tmem_st_x32(taddr, r);
+}
+
+template <int FMT, typename T, bool ATM, int DW>
+__global__ void __launch_bounds__(64 + 32 * DW, (ATM && DW == 8) ? 2 : 1)
 wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                   const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -267,6 +281,10 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   volatile int* abort_p = reinterpret_cast<volatile int*>(generic_base + (abort_slot - smem_base));
   volatile int* last_p = reinterpret_cast<volatile int*>(generic_base + (last_slot - smem_base));
 
+  constexpr int kDequantWarps = DW;
+  constexpr int kDequantThreads = 32 * DW;
+  constexpr int kSplit = DW / 4;                // K slices per weight row (2 or 4)
+  static_assert(ATM || DW == 8, "the shared-memory operand variant uses eight dequantise warps");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
@@ -281,21 +299,24 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   }
 #endif
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kMaxRing; ++i) {
-      mbar_init(p_full + 8 * i, 1);
-      mbar_init(p_empty + 8 * i, kDequantWarps);
-      mbar_init(a_full + 8 * i, kDequantWarps);
-      mbar_init(a_empty + 8 * i, 1);
-      mbar_init(x_full + 8 * i, 1);
-      mbar_init(x_empty + 8 * i, 1);
+  // barrier set-up spread over the lanes of warp 0 (one ring slot per lane)
+  if (warp == 0) {
+    if (lane < kMaxRing) {
+      mbar_init(p_full + 8 * lane, 1);
+      mbar_init(p_empty + 8 * lane, kDequantWarps);
+      mbar_init(a_full + 8 * lane, kDequantWarps);
+      mbar_init(a_empty + 8 * lane, 1);
+      mbar_init(x_full + 8 * lane, 1);
+      mbar_init(x_empty + 8 * lane, 1);
     }
-    mbar_init(acc_full, 1);
-    *abort_p = 0;
-    *last_p = 0;
+    if (lane == 0) {
+      mbar_init(acc_full, 1);
+      *abort_p = 0;
+      *last_p = 0;
+      tma_prefetch_desc(&tm_w);
+      tma_prefetch_desc(&tm_x);
+    }
     mbar_fence_init();
-    tma_prefetch_desc(&tm_w);
-    tma_prefetch_desc(&tm_x);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, static_cast<uint32_t>(p.tmem_cols));
@@ -446,7 +467,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int r_base = td >> 2;                // 0..63
     // A-in-TMEM mapping: a warp may only touch TMEM lanes 32*(warp%4)..+31
     const int atm_row = (warp & 3) * 32 + lane;
-    const int atm_kh = (warp - 2) >> 2;
+    const int atm_kq = (warp - 2) >> 2;                 // which K slice of the row
     const uint32_t atm_taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + p.a_col0;
     const int row_n0 = n_tile * kBlockN + (ATM ? atm_row : r_base);
     const int row_n1 = ATM ? p.N : row_n0 + 64;
@@ -509,7 +530,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (ATM) {
         // One thread = one output channel (its TMEM lane) x one 64-wide half of the K block.
         // The packed stage is read row-wise; the TMA 64-byte swizzle keeps that conflict-free.
-        const uint32_t prow = p_stage + (FMT == FMT_W8 ? atm_kh * (kBlockN * 64) : 0) + atm_row * 64;
+        const uint32_t prow = p_stage + atm_row * 64;
         const int xr = (atm_row >> 1) & 3;
         // fp16 activations: (1024 + n) - (1024 + zero) is exact, then ONE fp16 multiply by the
         // scale (the format's contract).  bf16 activations: the same in bf16, (128 + n) - (128 +
@@ -518,12 +539,15 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t a_stage_t = atm_taddr + sa * 64;
         if (td == 0 && i == 3) B200Q_STAMP(61);
         if (FMT == FMT_W4_REF) {
-          // This thread unpacks bytes 32*kh .. 32*kh+31 of its row: low nibbles are K offsets
-          // 32*kh + j (columns 16*kh..), high nibbles K offsets 64 + 32*kh + j (columns 32 + 16*kh..).
-          uint32_t lo[16], hi[16];
+          // This thread unpacks bytes [B*kq, B*kq + B) of its row, B = 64 / kSplit: low nibbles
+          // are K offsets B*kq + j (columns B/2*kq ..), high nibbles K offsets 64 + B*kq + j
+          // (columns 32 + B/2*kq ..).
+          constexpr int kVec = 4 / kSplit;               // 16-byte loads per thread
+          constexpr int kCols = 8 * kVec;                // columns per nibble half
+          uint32_t lo[kCols], hi[kCols];
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const uint4 v = ld_shared_v4(prow + (((2 * atm_kh + c) ^ xr) << 4));
+          for (int c = 0; c < kVec; ++c) {
+            const uint4 v = ld_shared_v4(prow + (((kVec * atm_kq + c) ^ xr) << 4));
             const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -536,15 +560,17 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               hi[(c * 4 + w) * 2 + 1] = deq_hi<kBf>(u >> 8, gp);
             }
           }
-          tmem_st_x16(a_stage_t + 16 * atm_kh, lo);
-          tmem_st_x16(a_stage_t + 32 + 16 * atm_kh, hi);
+          tmem_st_cols<kCols>(a_stage_t + kCols * atm_kq, lo);
+          tmem_st_cols<kCols>(a_stage_t + 32 + kCols * atm_kq, hi);
         } else if (FMT == FMT_W4_ASYM) {
-          // words 8*kh .. 8*kh+7 of the row: 64 consecutive K (columns 32*kh..); the layout's
+          // words [W*kq, W*kq + W) of the row, W = 16 / kSplit: 8 W consecutive K; the layout's
           // nibble order makes every lop3 pair a pair of K neighbours
-          uint32_t out[32];
+          constexpr int kVec = 4 / kSplit;
+          constexpr int kCols = 16 * kVec;
+          uint32_t out[kCols];
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const uint4 v = ld_shared_v4(prow + (((2 * atm_kh + c) ^ xr) << 4));
+          for (int c = 0; c < kVec; ++c) {
+            const uint4 v = ld_shared_v4(prow + (((kVec * atm_kq + c) ^ xr) << 4));
             const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -555,13 +581,18 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               out[(c * 4 + w) * 4 + 3] = deq_hi<kBf>(u >> 8, gp);   // inputs 6,7
             }
           }
-          tmem_st_x32(a_stage_t + 32 * atm_kh, out);
+          tmem_st_cols<kCols>(a_stage_t + kCols * atm_kq, out);
         } else {
-          // W8: sub-tile kh of the stage holds K offsets 64*kh .. 64*kh+63 of this row
-          uint32_t out[32];
+          // W8: the stage is two [128 x 64 B] sub-tiles (K 0..63, 64..127); this thread takes
+          // 128 / kSplit consecutive K of its row
+          constexpr int kVec = 8 / kSplit;               // 16 int8 per load
+          constexpr int kCols = 8 * kVec;
+          uint32_t out[kCols];
+          const int k_first = atm_kq * (128 / kSplit);   // first K of this thread's slice
+          const uint32_t sub = p_stage + (k_first >> 6) * (kBlockN * 64) + atm_row * 64;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 v = ld_shared_v4(prow + ((c ^ xr) << 4));
+          for (int c = 0; c < kVec; ++c) {
+            const uint4 v = ld_shared_v4(sub + (((((k_first & 63) >> 4) + c) ^ xr) << 4));
             const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -571,7 +602,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               out[(c * 4 + w) * 2 + 1] = pack_operand<T>(k23);
             }
           }
-          tmem_st_x32(a_stage_t + 32 * atm_kh, out);
+          tmem_st_cols<kCols>(a_stage_t + kCols * atm_kq, out);
         }
         if (td == 0 && i == 3) B200Q_STAMP(62);
         tmem_st_wait();
@@ -666,10 +697,10 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     acc_ok = __all_sync(0xffffffffu, acc_ok && !*abort_p) != 0;
     grid_dependency_wait();            // outputs and workspace belong to the stream order
     const int lane_quarter = warp & 3;                   // TMEM lanes this warp may read
-    const int col_half = (warp - 2) >> 2;                // which half of the token columns
+    const int col_half = (warp - 2) >> 2;                // which slice of the token columns
     const int ch = lane_quarter * 32 + lane;             // channel inside the tile
     const int n = n_tile * kBlockN + ch;
-    const int half_cols = p.tok >> 1;
+    const int half_cols = p.tok / kSplit;
     const int c_begin = col_half * half_cols;
     const int m_base = m_tile * p.tok;
     const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_quarter * 32) << 16);
@@ -756,7 +787,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (*last_p) {
         __threadfence();
         // Sum the partials of this tile in split order.  Flat mapping: a row of the tile is
-        // 128 channels = 32 float4; 8 rows per pass and 4 passes in flight per thread keep
+        // 128 channels = 32 float4; one row per warp and 4 passes in flight per thread keep
         // 4 x splits independent 16-byte loads outstanding (the partials sit in L2).
         const int n_base = n_tile * kBlockN;
         const int q4 = td & 31;                           // float4 index inside the row
@@ -773,7 +804,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             if (p.bias != nullptr) bs[e] = static_cast<float>(static_cast<const T*>(p.bias)[nq + e]);
           }
         }
-        for (int r0 = td >> 5; r0 < rows; r0 += 32) {
+        for (int r0 = td >> 5; r0 < rows; r0 += 4 * kDequantWarps) {
           float4 acc[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -781,7 +812,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             float4 t[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const int r = min(r0 + 8 * u, rows - 1);
+              const int r = min(r0 + kDequantWarps * u, rows - 1);
               const float* src = p.partial + (static_cast<int64_t>(z) * p.M + m_base + r) * p.N + nq;
               if (vec4) {
                 t[u] = __ldcg(reinterpret_cast<const float4*>(src));
@@ -802,7 +833,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const int r = r0 + 8 * u;
+            const int r = r0 + kDequantWarps * u;
             if (r < rows) {
               T* dst = yT + static_cast<int64_t>(m_base + r) * p.ldy + nq;
               const float v[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
@@ -923,6 +954,7 @@ constexpr int kMaxSplitTiles = static_cast<int>((kWsHeaderBytes - 256) / sizeof(
 
 struct TcPlan {
   int tok, m_tiles, n_tiles, kb_total, splits, kb_per_split, np, na, nx, pg, xg, tmem_cols, a_col0;
+  int dw;            // dequantise warps per block: 8, or 16 for wide tiles (one block per SM)
   bool atm;          // A operand in tensor memory (default) or in shared memory
   size_t smem_bytes;
 };
@@ -945,6 +977,14 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   const int mt = (M + 255) / 256;
   int tok = ((M + mt - 1) / mt + 15) / 16 * 16;
   if (tok < 16) tok = 16;
+  // Wide tiles own the whole SM: sixteen dequantise warps halve the latency of a dequantise
+  // stage there.  Each of their four column slices must be whole groups of 8 columns.
+  // Large prefill problems (many waves) are MMA-bound and measured no better with them.
+  pl.dw = 8;
+  if (pl.atm && tok > 64 && mt < 4) {
+    tok = (tok + 31) / 32 * 32;
+    pl.dw = 16;
+  }
   pl.tok = tok;
   pl.m_tiles = (M + tok - 1) / tok;
   pl.n_tiles = (N + kBlockN - 1) / kBlockN;
@@ -1070,7 +1110,7 @@ bool tc_supported(const ForwardArgs& a) {
   return true;
 }
 
-template <int FMT, typename T, bool ATM>
+template <int FMT, typename T, bool ATM, int DW>
 static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   static bool attr_set_dev[64] = {};
   static std::mutex attr_mu;
@@ -1080,7 +1120,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
     bool& attr_set = attr_set_dev[dev & 63];
     std::lock_guard<std::mutex> g(attr_mu);
     if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(wq_gemm_tc_kernel<FMT, T, ATM>,
+      cudaError_t e = cudaFuncSetAttribute(wq_gemm_tc_kernel<FMT, T, ATM, DW>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
       if (e != cudaSuccess) {
         set_last_error("cudaFuncSetAttribute", e);
@@ -1141,7 +1181,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   // kernel orders itself with griddepcontrol.wait before touching x, y or the workspace.
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.n_tiles, pl.m_tiles, pl.splits);
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(64 + 32 * DW);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
@@ -1149,7 +1189,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T, ATM>, tm_w, tm_x, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T, ATM, DW>, tm_w, tm_x, p);
   if (e != cudaSuccess) {
     set_last_error("cudaLaunchKernelEx", e);
     return B200Q_ERR_CUDA;
@@ -1159,7 +1199,8 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
 
 template <int FMT, typename T>
 static int launch_tc_operand(const ForwardArgs& a, const TcPlan& pl) {
-  return pl.atm ? launch_tc_typed<FMT, T, true>(a, pl) : launch_tc_typed<FMT, T, false>(a, pl);
+  if (!pl.atm) return launch_tc_typed<FMT, T, false, 8>(a, pl);
+  return pl.dw == 16 ? launch_tc_typed<FMT, T, true, 16>(a, pl) : launch_tc_typed<FMT, T, true, 8>(a, pl);
 }
 
 int launch_forward_tc(const ForwardArgs& a) {
