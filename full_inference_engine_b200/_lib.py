@@ -53,6 +53,27 @@ _SIGNATURES = {
                                                     _c_i64, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
 }
 
+
+
+class Gather(ctypes.Structure):
+    """``b200q_gather`` of include/b200q.h: peer-mapped output and signal pointers of every rank."""
+
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int),
+                ("y_peer", ctypes.c_void_p * 8), ("signal_peer", ctypes.c_void_p * 8)]
+
+
+_gather_p = ctypes.POINTER(Gather)
+_SIGNATURES.update({
+    "b200q_gather_tiles": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int]),
+    "b200q_w4a16_forward_gather": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_int, _c_void_p,
+                                            _c_void_p, _c_int, _c_void_p, _gather_p, _c_i64, _c_int, _c_int,
+                                            _c_int, _c_void_p, _c_size, _c_int, _c_void_p]),
+    "b200q_w8a16_forward_gather": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_void_p, _c_int,
+                                            _c_void_p, _gather_p, _c_i64, _c_int, _c_int, _c_int,
+                                            _c_void_p, _c_size, _c_int, _c_void_p]),
+    "b200q_gather_wait": (_c_int, [_gather_p, _c_int, _c_void_p]),
+})
+
 _lib = None
 _lock = threading.Lock()
 

@@ -174,4 +174,81 @@ int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype, const void* p
   return run_forward(a, kernel);
 }
 
+static int check_gather(const b200q_gather* g, int64_t ldy, int n_local) {
+  if (!g || g->world < 1 || g->world > 8 || g->rank < 0 || g->rank >= g->world) return B200Q_ERR_INVALID;
+  if (ldy < static_cast<int64_t>(g->world) * n_local) return B200Q_ERR_INVALID;
+  for (int r = 0; r < g->world; ++r) {
+    if (!g->y_peer[r] || !g->signal_peer[r]) return B200Q_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(g->signal_peer[r]) % 8) return B200Q_ERR_ALIGNMENT;
+  }
+  return B200Q_OK;
+}
+
+int b200q_gather_tiles(int format, int M, int N_local, int K, int group) {
+  if (format == 8) return (K % 64 == 0) ? tc_output_tiles(FMT_W8, M, N_local, K) : 0;
+  if (format == 4) return (group == 128 && K % 128 == 0) ? tc_output_tiles(FMT_W4_REF, M, N_local, K) : 0;
+  return 0;
+}
+
+int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const void* packed,
+                               int64_t ldw, int layout, const void* scales, const void* zeros,
+                               int group, const void* bias, const b200q_gather* gather, int64_t ldy,
+                               int M, int N_local, int K, void* workspace, size_t workspace_bytes,
+                               int flags, void* stream) {
+  if (M < 0 || N_local < 0 || K <= 0) return B200Q_ERR_INVALID;
+  if (M == 0 || N_local == 0) return B200Q_OK;
+  if (!x || !packed || !scales) return B200Q_ERR_INVALID;
+  if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (layout == B200Q_W4_ASYM_ZP_INT32) {
+    if (!zeros) return B200Q_ERR_INVALID;
+  } else if (layout != B200Q_W4_REF_SPLIT_HALF_SYM) {
+    return B200Q_ERR_INVALID;
+  }
+  if (group <= 0 || K % group) return B200Q_ERR_INVALID;
+  if (ldx < K || ldw < K / 2) return B200Q_ERR_INVALID;
+  if (int st = check_gather(gather, ldy, N_local)) return st;
+  ForwardArgs a{};
+  a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
+  a.w = packed; a.ldw = ldw;
+  a.format = layout == B200Q_W4_ASYM_ZP_INT32 ? FMT_W4_ASYM : FMT_W4_REF;
+  a.scales = scales; a.scale_dtype = B200Q_F16; a.zeros = zeros; a.group = group;
+  a.bias = bias; a.y = gather->y_peer[gather->rank]; a.ldy = ldy; a.M = M; a.N = N_local; a.K = K;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.gather = gather;
+  a.static_weights = (flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_forward_tc(a);
+}
+
+int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const int8_t* qweight,
+                               int64_t ldw, const void* scales, int scale_dtype, const void* bias,
+                               const b200q_gather* gather, int64_t ldy, int M, int N_local, int K,
+                               void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  if (M < 0 || N_local < 0 || K <= 0) return B200Q_ERR_INVALID;
+  if (M == 0 || N_local == 0) return B200Q_OK;
+  if (!x || !qweight || !scales) return B200Q_ERR_INVALID;
+  if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
+  if (ldx < K || ldw < K) return B200Q_ERR_INVALID;
+  if (int st = check_gather(gather, ldy, N_local)) return st;
+  ForwardArgs a{};
+  a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
+  a.w = qweight; a.ldw = ldw; a.format = FMT_W8;
+  a.scales = scales; a.scale_dtype = scale_dtype; a.zeros = nullptr; a.group = 0;
+  a.bias = bias; a.y = gather->y_peer[gather->rank]; a.ldy = ldy; a.M = M; a.N = N_local; a.K = K;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.gather = gather;
+  a.static_weights = (flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_forward_tc(a);
+}
+
+int b200q_gather_wait(const b200q_gather* gather, int tiles_per_rank, void* stream) {
+  if (!gather || gather->world < 1 || gather->world > 8 || tiles_per_rank <= 0) return B200Q_ERR_INVALID;
+  if (gather->rank < 0 || gather->rank >= gather->world || !gather->signal_peer[gather->rank])
+    return B200Q_ERR_INVALID;
+  return launch_gather_wait(gather, static_cast<unsigned long long>(tiles_per_rank) * gather->world,
+                            static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

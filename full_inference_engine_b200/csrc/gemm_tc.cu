@@ -63,6 +63,11 @@ struct TcParams {
   int pg, xg;        // K blocks per weight group / per activation chunk (one TMA each)
   float* partial;    // [splits, M, N] fp32 (split-K only)
   int static_weights;  // weights/scales/bias may be read ahead of the stream order
+  // fused all-gather (g_world > 1): every output tile is stored into the [M, ldy] buffer of
+  // every rank at column offset g_col0, through peer-mapped pointers
+  int g_world, g_rank, g_col0;
+  void* g_y[8];
+  unsigned long long* g_sig[8];   // each rank's signal block (see GatherSignal)
   unsigned* counters;  // [m_tiles * n_tiles], zero between launches
   unsigned* status;    // device status word (non-zero: a bounded wait expired)
 };
@@ -232,6 +237,43 @@ __device__ __forceinline__ void load_group_chunk(GroupChunk& g, const TcParams& 
       }
     }
   }
+}
+
+// Signal block of the fused all-gather, one per rank per output buffer (64-bit words):
+//   [0]     arrivals: +1 from every block of every rank that has stored a finished tile everywhere
+//   [1]     generation: calls completed on this rank (advanced by gather_wait_kernel)
+//   [2]     status: non-zero if a bounded wait of the protocol expired on this rank
+//   [8 + r] ready[r]: rank r has entered call number ready[r] (so its previous output is consumed)
+constexpr int kSigArrivals = 0, kSigGeneration = 1, kSigStatus = 2, kSigReady = 8;
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// After the forward of call `gen` on this rank: wait (bounded) until every block of every rank
+// has delivered its tiles here, then publish the new generation.
+__global__ void gather_wait_kernel(unsigned long long* sig, unsigned long long expected) {
+  if (threadIdx.x != 0) return;
+  const unsigned long long gen = sig[kSigGeneration] + 1;
+  bool ok = false;
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (ld_acquire_sys(sig + kSigArrivals) >= gen * expected) {
+      ok = true;
+      break;
+    }
+    __nanosleep(100);
+  }
+  if (!ok) sig[kSigStatus] = 1ull;
+  sig[kSigGeneration] = gen;
+  __threadfence_system();
 }
 
 // Column-count generic TMEM store of one thread's lane.
@@ -411,6 +453,13 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
+      if (p.g_world > 1 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        // Fused all-gather: tell every rank that this rank has entered call `gen`, i.e. that
+        // whatever read its previous output has finished (it precedes us in the stream).
+        grid_dependency_wait();
+        const unsigned long long gen = p.g_sig[p.g_rank][kSigGeneration] + 1;
+        for (int d = 0; d < p.g_world; ++d) st_release_sys(p.g_sig[d] + kSigReady + p.g_rank, gen);
+      }
       bool ok = true;
       int sa = 0, sx = 0, xs = 0;                // operand stage, activation chunk slot, block in chunk
       uint32_t a_phase = 0, x_phase = 0;
@@ -704,7 +753,42 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int c_begin = col_half * half_cols;
     const int m_base = m_tile * p.tok;
     const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_quarter * 32) << 16);
-    T* yT = static_cast<T*>(p.y);
+    // destinations: this rank's y, or with the fused all-gather the same tile in every rank's y
+    const bool gather = p.g_world > 1;
+    const int ndst = gather ? p.g_world : 1;
+    const int col0 = gather ? p.g_col0 : 0;
+    T* ydst[8];
+#pragma unroll
+    for (int d = 0; d < 8; ++d) ydst[d] = gather ? static_cast<T*>(p.g_y[d]) : static_cast<T*>(p.y);
+    // Before the first store into another rank's buffer: that rank must have entered this call
+    // (its consumer of the previous call is done).  Bounded; one thread polls, the rest wait at
+    // the named barrier.
+    auto gather_wait_ready = [&]() {
+      if (td == 0) {
+        unsigned long long* mine = p.g_sig[p.g_rank];
+        const unsigned long long gen = mine[kSigGeneration] + 1;
+        for (int d = 0; d < p.g_world; ++d) {
+          if (d == p.g_rank) continue;
+          bool ready = false;
+          for (uint32_t it = 0; it < (1u << 22); ++it) {
+            if (ld_acquire_sys(mine + kSigReady + d) >= gen) {
+              ready = true;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!ready) mine[kSigStatus] = 2ull;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+    };
+    // After the last store: make the tile visible system-wide, then count it on every rank.
+    auto gather_signal_done = [&]() {
+      __threadfence_system();
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      if (td == 0)
+        for (int d = 0; d < p.g_world; ++d) red_add_release_sys(p.g_sig[d] + kSigArrivals, 1ull);
+    };
     float ch_scale = 1.0f, ch_bias = 0.0f;
     if (n < p.N) {
       if (FMT == FMT_W8)
@@ -713,10 +797,12 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (p.bias != nullptr) ch_bias = static_cast<float>(static_cast<const T*>(p.bias)[n]);
     }
     if (p.splits == 1) {
+      if (gather) gather_wait_ready();
       // accumulators -> output dtype -> shared memory as [token][128 channels], then
       // 16-byte row-contiguous stores (the operand rings are idle by now)
       const uint32_t stage = x_ring;
-      const bool vec_out = (p.ldy % 8 == 0) && (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) &&
+      const bool vec_out = (p.ldy % 8 == 0) && (col0 % 8 == 0) &&
+                           (reinterpret_cast<uintptr_t>(ydst[0]) % 16 == 0) &&
                            (p.nx * x_chunk_bytes >= p.tok * 256);
       if (acc_ok && nkb > 0) {
         for (int c = 0; c < half_cols; c += 8) {
@@ -733,7 +819,8 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                            : "memory");
             } else {
               const int m = m_base + c_begin + c + j;
-              if (n < p.N && m < p.M) yT[static_cast<int64_t>(m) * p.ldy + n] = v;
+              if (n < p.N && m < p.M)
+                for (int d = 0; d < ndst; ++d) ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + n] = v;
             }
           }
         }
@@ -746,17 +833,21 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           const int rows = min(p.tok, p.M - m_base);
           for (int r = td >> 4; r < rows; r += kDequantThreads / 16) {
             const uint4 v = ld_shared_v4(stage + r * 256 + chunk * 16);
-            T* dst = yT + static_cast<int64_t>(m_base + r) * p.ldy + n_c;
-            if (n_c + 8 <= p.N) {
-              *reinterpret_cast<uint4*>(dst) = v;
-            } else {
-              const T* e = reinterpret_cast<const T*>(&v);
-              for (int k = 0; k < 8; ++k)
-                if (n_c + k < p.N) dst[k] = e[k];
+            const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + col0 + n_c;
+            for (int d = 0; d < ndst; ++d) {
+              T* dst = ydst[d] + off;
+              if (n_c + 8 <= p.N) {
+                *reinterpret_cast<uint4*>(dst) = v;
+              } else {
+                const T* e = reinterpret_cast<const T*>(&v);
+                for (int k = 0; k < 8; ++k)
+                  if (n_c + k < p.N) dst[k] = e[k];
+              }
             }
           }
         }
       }
+      if (gather) gather_signal_done();
       if (td == 0) B200Q_STAMP(57);
     } else {
       if (acc_ok && nkb > 0) {
@@ -786,6 +877,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
       if (*last_p) {
         __threadfence();
+        if (gather) gather_wait_ready();
         // Sum the partials of this tile in split order.  Flat mapping: a row of the tile is
         // 128 channels = 32 float4; one row per warp and 4 passes in flight per thread keep
         // 4 x splits independent 16-byte loads outstanding (the partials sit in L2).
@@ -835,14 +927,20 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           for (int u = 0; u < 4; ++u) {
             const int r = r0 + kDequantWarps * u;
             if (r < rows) {
-              T* dst = yT + static_cast<int64_t>(m_base + r) * p.ldy + nq;
+              const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + col0 + nq;
               const float v[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+              T o[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (nq + e < p.N) dst[e] = from_float<T>(v[e] * sc[e] + bs[e]);
+              for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
+              for (int d = 0; d < ndst; ++d) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (nq + e < p.N) ydst[d][off + e] = o[e];
+              }
             }
           }
         }
+        if (gather) gather_signal_done();
         if (td == 0) *counter = 0u;      // ready for the next launch / graph replay
       }
     }
@@ -1171,6 +1269,16 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.pg = pl.pg;
   p.xg = pl.xg;
   p.static_weights = a.static_weights ? 1 : 0;
+  p.g_world = 0;
+  if (a.gather != nullptr && a.gather->world > 1) {
+    p.g_world = a.gather->world;
+    p.g_rank = a.gather->rank;
+    p.g_col0 = a.gather->rank * a.N;
+    for (int d = 0; d < 8; ++d) {
+      p.g_y[d] = d < a.gather->world ? a.gather->y_peer[d] : nullptr;
+      p.g_sig[d] = d < a.gather->world ? static_cast<unsigned long long*>(a.gather->signal_peer[d]) : nullptr;
+    }
+  }
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   p.status = reinterpret_cast<unsigned*>(ws);
   p.counters = reinterpret_cast<unsigned*>(ws + 256);
@@ -1201,6 +1309,18 @@ template <int FMT, typename T>
 static int launch_tc_operand(const ForwardArgs& a, const TcPlan& pl) {
   if (!pl.atm) return launch_tc_typed<FMT, T, false, 8>(a, pl);
   return pl.dw == 16 ? launch_tc_typed<FMT, T, true, 16>(a, pl) : launch_tc_typed<FMT, T, true, 8>(a, pl);
+}
+
+int tc_output_tiles(int format, int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const TcPlan pl = make_plan(format, M, N, K);
+  return pl.m_tiles * pl.n_tiles;
+}
+
+int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream) {
+  gather_wait_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned long long*>(g->signal_peer[g->rank]),
+                                           expected);
+  return note_launch();
 }
 
 int launch_forward_tc(const ForwardArgs& a) {

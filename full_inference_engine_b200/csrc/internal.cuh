@@ -32,6 +32,7 @@ struct ForwardArgs {
   void* workspace;
   size_t workspace_bytes;
   bool static_weights;  // weights/scales/zeros/bias were written long before this call
+  const b200q_gather* gather;  // fused all-gather destinations, or null
   cudaStream_t stream;
 };
 
@@ -55,5 +56,7 @@ int launch_forward_simt(const ForwardArgs& a);
 bool tc_supported(const ForwardArgs& a);
 size_t tc_workspace_bytes(int format, int M, int N, int K);
 int launch_forward_tc(const ForwardArgs& a);
+int tc_output_tiles(int format, int M, int N, int K);
+int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream);
 
 }  // namespace b200q

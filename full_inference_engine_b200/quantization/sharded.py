@@ -11,6 +11,7 @@ one ``all_gather`` (NCCL over NVLink on GPUs, gloo in the CPU tests).
 from __future__ import annotations
 
 import copy
+import ctypes
 
 import torch
 import torch.distributed as dist
@@ -55,19 +56,107 @@ def shard_quantized_linear(module: nn.Module, rank: int, world: int) -> nn.Modul
 
 
 class ColumnParallelLinear(nn.Module):
-    """This rank's shard plus the all-gather that rebuilds ``[..., N]`` on every rank."""
+    """This rank's shard plus the all-gather that rebuilds ``[..., N]`` on every rank.
+
+    ``fused=True`` (CUDA, NVLink peers) replaces "kernel, then NCCL all-gather" by one kernel
+    whose epilogue stores each finished tile straight into every rank's output buffer through
+    peer-mapped pointers, followed by a tiny wait kernel.  The output is then a persistent
+    symmetric-memory buffer per row count (returned as is: copy it if you need it beyond the
+    next call with the same row count), allocated on first use by a rendezvous that every rank
+    must reach, so all ranks must call with the same sequence of shapes.
+    """
 
     def __init__(self, local: nn.Module, *, world: int | None = None, group=None,
-                 gather: bool = True):
+                 gather: bool = True, fused: bool = False):
         super().__init__()
         self.local = local
         self.group = group
         self.world = world if world is not None else dist.get_world_size(group)
         self.gather = gather
+        self.fused = fused
         self.in_features = local.in_features
         self.out_features = local.out_features * self.world
+        self._buffers_by_rows: dict = {}
+
+    # ------------------------------------------------------------------ fused path
+    def _symmetric_output(self, rows: int, dtype: torch.dtype, device: torch.device):
+        key = (rows, dtype)
+        held = self._buffers_by_rows.get(key)
+        if held is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("first fused call for this row count must happen outside "
+                                   "CUDA-graph capture (it allocates symmetric memory)")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            from .. import _lib
+
+            group = self.group if self.group is not None else dist.group.WORLD
+            out = symm_mem.empty((rows, self.out_features), dtype=dtype, device=device)
+            handle = symm_mem.rendezvous(out, group)
+            desc = _lib.Gather()
+            desc.rank, desc.world = handle.rank, handle.world_size
+            for r in range(handle.world_size):
+                desc.y_peer[r] = handle.buffer_ptrs[r]
+                desc.signal_peer[r] = handle.signal_pad_ptrs[r]
+            held = (out, handle, desc)
+            self._buffers_by_rows[key] = held
+        return held
+
+    def _fused_forward(self, x: torch.Tensor) -> torch.Tensor | None:
+        from .. import _lib
+
+        local = self.local
+        rows = x.reshape(-1, self.in_features)
+        if rows.dtype not in (torch.float16, torch.bfloat16) or rows.device.type != "cuda":
+            return None
+        is_w4 = isinstance(local, W4A16Linear)
+        m, k, n_local = rows.shape[0], self.in_features, local.out_features
+        lib = _lib.library()
+        tiles = lib.b200q_gather_tiles(4 if is_w4 else 8, m, n_local, k,
+                                       local.group_size if is_w4 else 0)
+        if tiles <= 0 or getattr(local, "reference", False) or m == 0:
+            return None
+        if rows.stride(1) != 1 or rows.stride(0) % 8 or rows.data_ptr() % 16:
+            rows = rows.contiguous()
+        out, _handle, desc = self._symmetric_output(m, rows.dtype, rows.device)
+        ws = _lib.workspace_for(rows.device, _lib.workspace_bytes(4 if is_w4 else 8, m, n_local, k))
+        stream = _lib.stream_ptr(rows.device)
+        bias = None if local.bias is None else local.bias.to(rows.dtype).contiguous()
+        with torch.cuda.device(rows.device):
+            if is_w4:
+                _lib.check(lib.b200q_w4a16_forward_gather(
+                    rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
+                    local.packed.data_ptr(), local.packed.stride(0), _lib.W4_REF_SPLIT_HALF_SYM,
+                    local.scales.data_ptr(), None, local.group_size,
+                    None if bias is None else bias.data_ptr(),
+                    ctypes.byref(desc), out.stride(0), m, n_local, k,
+                    ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                    "b200q_w4a16_forward_gather")
+            else:
+                _lib.check(lib.b200q_w8a16_forward_gather(
+                    rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
+                    local.qweight.data_ptr(), local.qweight.stride(0),
+                    local.scales.data_ptr(), _lib.dtype_enum(local.scales.dtype),
+                    None if bias is None else bias.data_ptr(),
+                    ctypes.byref(desc), out.stride(0), m, n_local, k,
+                    ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                    "b200q_w8a16_forward_gather")
+            _lib.check(lib.b200q_gather_wait(ctypes.byref(desc), tiles, stream), "b200q_gather_wait")
+        return out.reshape(*x.shape[:-1], self.out_features)
+
+    def gather_status(self) -> int:
+        """Non-zero if a bounded wait of the fused protocol ever expired on this rank."""
+        status = 0
+        for out, handle, _desc in self._buffers_by_rows.values():
+            pad = handle.get_signal_pad(handle.rank, (8,), torch.int64)
+            status |= int(pad[2].item())
+        return status
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.fused and self.gather and self.world > 1:
+            out = self._fused_forward(x)
+            if out is not None:
+                return out
         y = self.local(x)
         if not self.gather or self.world == 1:
             return y

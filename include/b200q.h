@@ -186,6 +186,58 @@ int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype,
                         int kernel, void* stream);
 
 /*
+ * Fused column-parallel forward + all-gather (no reference counterpart: the reference
+ * is single-GPU).  Rank `rank` of `world` (<= 8) holds N_local = N/world output rows
+ * of the weights; instead of writing y[M, N_local] and calling a collective, the
+ * kernel's epilogue stores every finished tile into the full [M, ldy] output of
+ * EVERY rank at columns [rank*N_local, (rank+1)*N_local) through peer-mapped
+ * pointers (plain stores over NVLink; no multicast loads anywhere).
+ *   y_peer[r]       peer-mapped base of rank r's full output buffer (same shape on all ranks)
+ *   signal_peer[r]  peer-mapped base of rank r's signal block: >= 256 bytes, 8-byte
+ *                   aligned, zero-filled once when the buffer is created, never
+ *                   touched by the host afterwards
+ * Protocol per call: the kernel announces "this rank has entered the call" to all
+ * ranks, waits (bounded) for the same announcement from a rank before its first
+ * store into that rank's buffer, and counts each delivered tile on every rank.
+ * b200q_gather_wait, enqueued after the forward on the same stream, waits (bounded)
+ * until all world * b200q_gather_tiles() tiles have arrived, which makes the full
+ * output safe to read by later work in the stream.  Every rank must make the same
+ * sequence of calls on a given buffer.  A bounded wait that expires sets the status
+ * word of the signal block (64-bit word 2) instead of hanging.
+ * The tensor-core kernel serves these calls: geometries it does not take
+ * (b200q_gather_tiles() == 0) must use a separate collective.
+ */
+typedef struct b200q_gather {
+  int rank;
+  int world;
+  void* y_peer[8];
+  void* signal_peer[8];
+} b200q_gather;
+
+/* Output tiles one rank's forward of this geometry delivers (0: not supported fused). */
+int b200q_gather_tiles(int format, int M, int N_local, int K, int group);
+
+int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype,
+                               const void* packed, int64_t ldw, int layout,
+                               const void* scales, const void* zeros, int group,
+                               const void* bias,
+                               const b200q_gather* gather, int64_t ldy,
+                               int M, int N_local, int K,
+                               void* workspace, size_t workspace_bytes,
+                               int flags, void* stream);
+
+int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype,
+                               const int8_t* qweight, int64_t ldw,
+                               const void* scales, int scale_dtype,
+                               const void* bias,
+                               const b200q_gather* gather, int64_t ldy,
+                               int M, int N_local, int K,
+                               void* workspace, size_t workspace_bytes,
+                               int flags, void* stream);
+
+int b200q_gather_wait(const b200q_gather* gather, int tiles_per_rank, void* stream);
+
+/*
  * The INT4 forward for callers that have no device memory to give: same
  * arguments and results as b200q_w4a16_forward, minus the workspace.  It has no
  * counterpart in the reference.  It exists for hosts that cannot allocate on the
