@@ -343,7 +343,9 @@ def config_dict(args, cases, rotation):
                    "ref": "reference split-half uint8 + fp16 scale"}[args.layout]
         if cases[0].fmt != "w8" else "int8 per-channel fp16 scale",
         "cases": len(cases),
-        "parallelism": f"N-sharded x{args.gpus} + all-gather" if args.gpus > 1 else "single GPU",
+        "parallelism": (f"N-sharded x{args.gpus}, all-gather "
+                        + ("fused into the kernel epilogue (peer stores over NVLink)"
+                           if args.gather == "fused" else "by NCCL")) if args.gpus > 1 else "single GPU",
         "l2": rotation,
     }
 
@@ -393,15 +395,39 @@ def run_b200(args, cases):
     local_cases = [Case(c.name, c.fmt, c.m, c.k, c.n // world, c.dtype, c.outliers) for c in cases]
     gathered = [torch.empty(world, c.m, c.n // world, dtype=c.dtype, device=device) if world > 1 else None
                 for c in cases]
+    # fused all-gather: full [M, N] outputs in symmetric memory, written by every rank's epilogue
+    fused_out = None
+    if world > 1 and args.gather == "fused":
+        from full_inference_engine_b200.quantization.sharded import SymmetricOutput
+
+        fused_out = [SymmetricOutput(c.m, c.n, c.dtype, device) for c in cases]
+
+    def forward_gather(i, case, x, w):
+        """This rank's columns of case i delivered to every rank; returns the local view."""
+        if fused_out is not None:
+            from full_inference_engine_b200.quantization.sharded import fused_forward_gather
+
+            if case.fmt == "w8":
+                ok = fused_forward_gather(x, fused_out[i], qweight=w[0], scales=w[1])
+            elif case.fmt == "w4_ref":
+                ok = fused_forward_gather(x, fused_out[i], packed=w[0], scales=w[1])
+            else:
+                ok = fused_forward_gather(x, fused_out[i], packed=w[0], scales=w[1], zeros=w[2])
+            if ok:
+                return fused_out[i].tensor
+        y = forward(case, x, w)
+        dist.all_gather_into_tensor(gathered[i], y)
+        return y
 
     def one_step(variant: int, gather: bool = True):
         outs = []
         for i, case in enumerate(local_cases):
             sets = weight_sets[(case.fmt, case.name)]
             w = sets[(i + variant * len(local_cases)) % len(sets)]
-            y = forward(case, acts[i], w)
             if world > 1 and gather:
-                dist.all_gather_into_tensor(gathered[i], y)
+                y = forward_gather(i, case, acts[i], w)
+            else:
+                y = forward(case, acts[i], w)
             outs.append(y)
         return outs
 
@@ -424,17 +450,17 @@ def run_b200(args, cases):
 
     # ---- end to end (measured before any graph holds NCCL work): pinned host activations in, host results out, through the public API
     host_x = [torch.empty(c.m, c.k, dtype=c.dtype).pin_memory().copy_(acts[i].cpu()) for i, c in enumerate(cases)]
-    host_y = [torch.empty(c.m, c.n // world, dtype=c.dtype).pin_memory() for c in cases]
+    host_y = [torch.empty(c.m, c.n if fused_out is not None else c.n // world, dtype=c.dtype).pin_memory()
+              for c in cases]
     dev_x = [torch.empty_like(a) for a in acts]
 
     def e2e_step(variant):
         for i, case in enumerate(local_cases):
             dev_x[i].copy_(host_x[i], non_blocking=True)
             sets = weight_sets[(case.fmt, case.name)]
-            y = forward(case, dev_x[i], sets[(i + variant * len(local_cases)) % len(sets)])
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[i], y)
-            host_y[i].copy_(y, non_blocking=True)
+            w = sets[(i + variant * len(local_cases)) % len(sets)]
+            y = forward_gather(i, case, dev_x[i], w) if world > 1 else forward(case, dev_x[i], w)
+            host_y[i].copy_(y if y.shape[-1] == case.n else y, non_blocking=True)
         torch.cuda.synchronize()          # the step's results are on the host
         return float(host_y[-1][0, 0])
 
@@ -569,6 +595,8 @@ def run_b200(args, cases):
     note("per-case timing done")
 
     status = _lib.library().b200q_workspace_status(_lib.workspace_for(device, 256).data_ptr(), None)
+    if fused_out is not None:      # a bounded wait of the fused gather protocol expired somewhere
+        status = status or (7 if any(o.status() for o in fused_out) else 0)
 
     if rank == 0:
         total_bytes = sum(c.bytes for c in cases)          # whole job, all ranks
@@ -590,7 +618,7 @@ def run_b200(args, cases):
             "e2e": {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                     "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": int(sum(2 * c.m * c.k for c in cases)),
-                    "d2h_bytes_per_step": int(sum(2 * c.m * (c.n // world) for c in cases)),
+                    "d2h_bytes_per_step": int(sum(hy.numel() * hy.element_size() for hy in host_y)),
                     "note": "weights stay resident on the device (module state); activations come "
                             "from pinned host memory and results return to it every step"},
             "gpu_launches": int(launches_per_step * args.steps),
@@ -642,6 +670,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="at --gpus > 1: all-gather inside the kernel epilogue, or a NCCL call after it")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--profile", action="store_true",
                     help="eager launches of the selected cases only (for ncu): no graphs, no e2e, no CPU leg")

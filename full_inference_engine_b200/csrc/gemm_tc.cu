@@ -254,24 +254,35 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ void red_add_release_sys(unsigned long long* p, unsigned long long v) {
-  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ void red_add_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Bounded system-scope poll: quick at first, then about a microsecond per look, roughly five
+// seconds in all.  Ranks are separate processes, so benign host-side skew (a first-call
+// set-up, a garbage collection) has to fit inside the bound; a rank that never arrives makes
+// the caller record a status and move on instead of hanging.
+__device__ __forceinline__ bool poll_at_least(const unsigned long long* p, unsigned long long target) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (ld_acquire_sys(p) >= target) return true;
+    __nanosleep(i < 4096 ? 40 : 1000);
+  }
+  return false;
 }
 
 // After the forward of call `gen` on this rank: wait (bounded) until every block of every rank
 // has delivered its tiles here, then publish the new generation.
 __global__ void gather_wait_kernel(unsigned long long* sig, unsigned long long expected) {
   if (threadIdx.x != 0) return;
+  // Launched with programmatic stream serialization so that the kernel AFTER it may begin its
+  // prologue (and stream static weights) at once; that kernel's griddepcontrol.wait still
+  // holds it until this one has finished.  This kernel itself first waits for the forward
+  // before it to complete: the generation word it reads is written by the previous wait
+  // kernel, which that forward was ordered behind.
+  grid_launch_dependents();
+  grid_dependency_wait();
   const unsigned long long gen = sig[kSigGeneration] + 1;
-  bool ok = false;
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (ld_acquire_sys(sig + kSigArrivals) >= gen * expected) {
-      ok = true;
-      break;
-    }
-    __nanosleep(100);
-  }
-  if (!ok) sig[kSigStatus] = 1ull;
+  if (!poll_at_least(sig + kSigArrivals, gen * expected)) sig[kSigStatus] = 1ull;
   sig[kSigGeneration] = gen;
   __threadfence_system();
 }
@@ -769,25 +780,20 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const unsigned long long gen = mine[kSigGeneration] + 1;
         for (int d = 0; d < p.g_world; ++d) {
           if (d == p.g_rank) continue;
-          bool ready = false;
-          for (uint32_t it = 0; it < (1u << 22); ++it) {
-            if (ld_acquire_sys(mine + kSigReady + d) >= gen) {
-              ready = true;
-              break;
-            }
-            __nanosleep(100);
-          }
-          if (!ready) mine[kSigStatus] = 2ull;
+          if (!poll_at_least(mine + kSigReady + d, gen)) mine[kSigStatus] = 2ull;
         }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
     };
     // After the last store: make the tile visible system-wide, then count it on every rank.
+    // The block barrier orders every thread's stores before thread 0's system-scope fence
+    // (fences are cumulative), so one fence per block covers the whole tile.
     auto gather_signal_done = [&]() {
-      __threadfence_system();
       asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
-      if (td == 0)
-        for (int d = 0; d < p.g_world; ++d) red_add_release_sys(p.g_sig[d] + kSigArrivals, 1ull);
+      if (td == 0) {
+        __threadfence_system();
+        for (int d = 0; d < p.g_world; ++d) red_add_relaxed_sys(p.g_sig[d] + kSigArrivals, 1ull);
+      }
     };
     float ch_scale = 1.0f, ch_bias = 0.0f;
     if (n < p.N) {
@@ -1318,8 +1324,22 @@ int tc_output_tiles(int format, int M, int N, int K) {
 }
 
 int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream) {
-  gather_wait_kernel<<<1, 32, 0, stream>>>(static_cast<unsigned long long*>(g->signal_peer[g->rank]),
-                                           expected);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gather_wait_kernel,
+                                     static_cast<unsigned long long*>(g->signal_peer[g->rank]), expected);
+  if (e != cudaSuccess) {
+    set_last_error("cudaLaunchKernelEx(gather_wait)", e);
+    return B200Q_ERR_CUDA;
+  }
   return note_launch();
 }
 

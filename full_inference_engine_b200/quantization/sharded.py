@@ -55,6 +55,76 @@ def shard_quantized_linear(module: nn.Module, rank: int, world: int) -> nn.Modul
     raise TypeError(f"cannot shard {type(module).__name__}")
 
 
+class SymmetricOutput:
+    """A full ``[rows, N]`` output buffer in symmetric memory plus its peer pointers.
+
+    Creating one is a rendezvous: every rank of ``group`` must create the same buffer at the
+    same point of its program.  Never create one inside a CUDA-graph capture.
+    """
+
+    def __init__(self, rows: int, out_features: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .. import _lib
+
+        group = group if group is not None else dist.group.WORLD
+        self.tensor = symm_mem.empty((rows, out_features), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        self.desc = _lib.Gather()
+        self.desc.rank, self.desc.world = self.handle.rank, self.handle.world_size
+        for r in range(self.handle.world_size):
+            self.desc.y_peer[r] = self.handle.buffer_ptrs[r]
+            self.desc.signal_peer[r] = self.handle.signal_pad_ptrs[r]
+
+    def status(self) -> int:
+        """Non-zero if a bounded wait of the fused protocol expired on this rank."""
+        pad = self.handle.get_signal_pad(self.handle.rank, (8,), torch.int64)
+        return int(pad[2].item())
+
+
+def fused_forward_gather(rows: torch.Tensor, out: SymmetricOutput, *, qweight=None, packed=None,
+                         scales=None, zeros=None, bias=None, group_size: int = 128) -> bool:
+    """One kernel computes this rank's columns and stores them into every rank's ``out``;
+    a wait kernel then holds the stream until all ranks' columns have arrived here.
+
+    Pass ``qweight`` (int8) for W8A16 or ``packed`` (uint8 reference layout, or int32 with
+    ``zeros`` for the asymmetric layout) for INT4; the tensors hold this rank's rows only.
+    Returns False (nothing launched) when the tensor-core kernel does not take the geometry.
+    """
+    from .. import _lib
+
+    lib = _lib.library()
+    m, k = rows.shape
+    is_w4 = packed is not None
+    n_local = (packed if is_w4 else qweight).shape[0]
+    tiles = lib.b200q_gather_tiles(4 if is_w4 else 8, m, n_local, k, group_size if is_w4 else 0)
+    if tiles <= 0 or m == 0:
+        return False
+    ws = _lib.workspace_for(rows.device, _lib.workspace_bytes(4 if is_w4 else 8, m, n_local, k))
+    stream = _lib.stream_ptr(rows.device)
+    bias_ptr = None if bias is None else bias.data_ptr()
+    with torch.cuda.device(rows.device):
+        if is_w4:
+            layout = _lib.W4_REF_SPLIT_HALF_SYM if zeros is None else _lib.W4_ASYM_ZP_INT32
+            _lib.check(lib.b200q_w4a16_forward_gather(
+                rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
+                packed.data_ptr(), packed.stride(0) * packed.element_size(), layout,
+                scales.data_ptr(), None if zeros is None else zeros.data_ptr(), group_size, bias_ptr,
+                ctypes.byref(out.desc), out.tensor.stride(0), m, n_local, k,
+                ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                "b200q_w4a16_forward_gather")
+        else:
+            _lib.check(lib.b200q_w8a16_forward_gather(
+                rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
+                qweight.data_ptr(), qweight.stride(0), scales.data_ptr(),
+                _lib.dtype_enum(scales.dtype), bias_ptr,
+                ctypes.byref(out.desc), out.tensor.stride(0), m, n_local, k,
+                ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                "b200q_w8a16_forward_gather")
+        _lib.check(lib.b200q_gather_wait(ctypes.byref(out.desc), tiles, stream), "b200q_gather_wait")
+    return True
+
+
 class ColumnParallelLinear(nn.Module):
     """This rank's shard plus the all-gather that rebuilds ``[..., N]`` on every rank.
 
@@ -79,77 +149,40 @@ class ColumnParallelLinear(nn.Module):
         self._buffers_by_rows: dict = {}
 
     # ------------------------------------------------------------------ fused path
-    def _symmetric_output(self, rows: int, dtype: torch.dtype, device: torch.device):
+    def _symmetric_output(self, rows: int, dtype: torch.dtype, device: torch.device) -> SymmetricOutput:
         key = (rows, dtype)
         held = self._buffers_by_rows.get(key)
         if held is None:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("first fused call for this row count must happen outside "
                                    "CUDA-graph capture (it allocates symmetric memory)")
-            import torch.distributed._symmetric_memory as symm_mem
-
-            from .. import _lib
-
-            group = self.group if self.group is not None else dist.group.WORLD
-            out = symm_mem.empty((rows, self.out_features), dtype=dtype, device=device)
-            handle = symm_mem.rendezvous(out, group)
-            desc = _lib.Gather()
-            desc.rank, desc.world = handle.rank, handle.world_size
-            for r in range(handle.world_size):
-                desc.y_peer[r] = handle.buffer_ptrs[r]
-                desc.signal_peer[r] = handle.signal_pad_ptrs[r]
-            held = (out, handle, desc)
+            held = SymmetricOutput(rows, self.out_features, dtype, device, self.group)
             self._buffers_by_rows[key] = held
         return held
 
     def _fused_forward(self, x: torch.Tensor) -> torch.Tensor | None:
-        from .. import _lib
-
         local = self.local
         rows = x.reshape(-1, self.in_features)
         if rows.dtype not in (torch.float16, torch.bfloat16) or rows.device.type != "cuda":
             return None
-        is_w4 = isinstance(local, W4A16Linear)
-        m, k, n_local = rows.shape[0], self.in_features, local.out_features
-        lib = _lib.library()
-        tiles = lib.b200q_gather_tiles(4 if is_w4 else 8, m, n_local, k,
-                                       local.group_size if is_w4 else 0)
-        if tiles <= 0 or getattr(local, "reference", False) or m == 0:
+        if getattr(local, "reference", False) or rows.shape[0] == 0:
             return None
         if rows.stride(1) != 1 or rows.stride(0) % 8 or rows.data_ptr() % 16:
             rows = rows.contiguous()
-        out, _handle, desc = self._symmetric_output(m, rows.dtype, rows.device)
-        ws = _lib.workspace_for(rows.device, _lib.workspace_bytes(4 if is_w4 else 8, m, n_local, k))
-        stream = _lib.stream_ptr(rows.device)
+        out = self._symmetric_output(rows.shape[0], rows.dtype, rows.device)
         bias = None if local.bias is None else local.bias.to(rows.dtype).contiguous()
-        with torch.cuda.device(rows.device):
-            if is_w4:
-                _lib.check(lib.b200q_w4a16_forward_gather(
-                    rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
-                    local.packed.data_ptr(), local.packed.stride(0), _lib.W4_REF_SPLIT_HALF_SYM,
-                    local.scales.data_ptr(), None, local.group_size,
-                    None if bias is None else bias.data_ptr(),
-                    ctypes.byref(desc), out.stride(0), m, n_local, k,
-                    ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
-                    "b200q_w4a16_forward_gather")
-            else:
-                _lib.check(lib.b200q_w8a16_forward_gather(
-                    rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
-                    local.qweight.data_ptr(), local.qweight.stride(0),
-                    local.scales.data_ptr(), _lib.dtype_enum(local.scales.dtype),
-                    None if bias is None else bias.data_ptr(),
-                    ctypes.byref(desc), out.stride(0), m, n_local, k,
-                    ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
-                    "b200q_w8a16_forward_gather")
-            _lib.check(lib.b200q_gather_wait(ctypes.byref(desc), tiles, stream), "b200q_gather_wait")
-        return out.reshape(*x.shape[:-1], self.out_features)
+        if isinstance(local, W4A16Linear):
+            done = fused_forward_gather(rows, out, packed=local.packed, scales=local.scales, bias=bias,
+                                        group_size=local.group_size)
+        else:
+            done = fused_forward_gather(rows, out, qweight=local.qweight, scales=local.scales, bias=bias)
+        return out.tensor.reshape(*x.shape[:-1], self.out_features) if done else None
 
     def gather_status(self) -> int:
         """Non-zero if a bounded wait of the fused protocol ever expired on this rank."""
         status = 0
-        for out, handle, _desc in self._buffers_by_rows.values():
-            pad = handle.get_signal_pad(handle.rank, (8,), torch.int64)
-            status |= int(pad[2].item())
+        for held in self._buffers_by_rows.values():
+            status |= held.status()
         return status
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
