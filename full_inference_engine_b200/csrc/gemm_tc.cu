@@ -26,7 +26,9 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <tuple>
 #include <type_traits>
 #include <unordered_map>
 
@@ -59,6 +61,7 @@ struct TcParams {
   int kb_total;      // ceil(K / 128)
   int kb_per_split;
   int splits;
+  int cluster_reduce;  // split-K partials are summed over distributed shared memory (cluster = the splits of a tile)
   int np, na, nx;    // ring depths: weight groups, operand stages, activation chunks
   int pg, xg;        // K blocks per weight group / per activation chunk (one TMA each)
   float* partial;    // [splits, M, N] fp32 (split-K only)
@@ -145,6 +148,26 @@ __device__ __forceinline__ unsigned long long global_ns() {
   do {                                                                                 \
     if (trace_cta < 1024 && (slot) < 64) g_trace[trace_cta * 64 + (slot)] = clock64(); \
   } while (0)
+// cumulative per-phase cycle counters of one dequantise warp (slots 40..47)
+#define B200Q_TIMER_DECL long long tmr_last = clock64(), tmr_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define B200Q_TIMER_LAP(k)                  \
+  {                                         \
+    const long long tmr_now = clock64();    \
+    tmr_acc[k] += tmr_now - tmr_last;       \
+    tmr_last = tmr_now;                     \
+  }
+#define B200Q_TIMER_RESET(on)                  \
+  if (on) {                                    \
+    for (int k = 0; k < 8; ++k) tmr_acc[k] = 0; \
+  }
+#define B200Q_TIMER_FLUSH(on)                                                                \
+  if (on) {                                                                                  \
+    for (int k = 0; k < 8; ++k) g_trace[(trace_cta & 1023) * 64 + 40 + k] = tmr_acc[k];      \
+  }
+#define B200Q_TIMER_FLUSH_MMA                                                                \
+  {                                                                                          \
+    for (int k = 0; k < 4; ++k) g_trace[(trace_cta & 1023) * 64 + 48 + k] = tmr_acc[k];      \
+  }
 #define B200Q_STAMP_NS(slot)                                                             \
   do {                                                                                   \
     if (trace_cta < 1024 && (slot) < 64) g_trace[trace_cta * 64 + (slot)] = global_ns(); \
@@ -152,6 +175,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
 #else
 #define B200Q_STAMP(slot)
 #define B200Q_STAMP_NS(slot)
+#define B200Q_TIMER_DECL
+#define B200Q_TIMER_LAP(k)
+#define B200Q_TIMER_RESET(on)
+#define B200Q_TIMER_FLUSH(on)
+#define B200Q_TIMER_FLUSH_MMA
 #endif
 
 // Per-(row, group) parameters of the 4-bit formats, fetched eight groups at a time
@@ -474,13 +502,18 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       bool ok = true;
       int sa = 0, sx = 0, xs = 0;                // operand stage, activation chunk slot, block in chunk
       uint32_t a_phase = 0, x_phase = 0;
+      B200Q_TIMER_DECL
       for (int i = 0; i < nkb && ok; ++i) {
+        B200Q_TIMER_LAP(3)
+        B200Q_TIMER_RESET(i == 1)
         if (xs == 0) {
           ok = wait_or_abort(x_full + 8 * sx, x_phase, abort_p);
           if (!ok) break;
         }
+        B200Q_TIMER_LAP(0)
         ok = wait_or_abort(a_full + 8 * sa, a_phase, abort_p);
         if (!ok) break;
+        B200Q_TIMER_LAP(1)
         tc_fence_after_sync();
         if (i < 6) B200Q_STAMP(8 + 2 * i);
         const uint32_t a_stage = a_ring + sa * kStageBytesA;
@@ -505,6 +538,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         umma_commit(a_empty + 8 * sa);
         if (xs == p.xg - 1 || i == nkb - 1) umma_commit(x_empty + 8 * sx);
         if (i < 6) B200Q_STAMP(9 + 2 * i);
+        B200Q_TIMER_LAP(2)
         if (++sa == p.na) {
           sa = 0;
           a_phase ^= 1;
@@ -517,6 +551,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
         }
       }
+      B200Q_TIMER_FLUSH_MMA
       if (!ok) flag_failure(abort_p, p.status, 2u);
       umma_commit(acc_full);
     }
@@ -543,7 +578,9 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     bool ok = true;
     int sp = 0, ps = 0, sa = 0;                  // weight group slot, block in group, operand stage
     uint32_t p_phase = 0, a_phase = 1;           // parities: p_full, a_empty
+    B200Q_TIMER_DECL
     for (int i = 0; i < nkb && ok; ++i) {
+      B200Q_TIMER_LAP(4)
       const int kb = kb0 + i;
       __half2 scale2[2];
       __half2 bias_lo[2], nbias_hi[2];
@@ -564,6 +601,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
       }
       if (td == 0 && i == 3) B200Q_STAMP(5);
+      B200Q_TIMER_LAP(7)
       PairConsts gp{0u, 0u, 0u};
       if (ATM && FMT != FMT_W8) {
         const int idx = ((p.groups & 7) == 0) ? (kb & 7) : 0;
@@ -579,11 +617,14 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           gp.scale = as_u32(__half2half2(sh));
         }
       }
+      B200Q_TIMER_LAP(0)
       if (ps == 0) ok = wait_or_abort(p_full + 8 * sp, p_phase, abort_p);
+      B200Q_TIMER_LAP(1)
       if (td == 0 && i == 3) B200Q_STAMP(6);
       ok = ok && wait_or_abort(a_empty + 8 * sa, a_phase, abort_p);
       if (!ok) break;
-      if (td == 0 && i < 12) B200Q_STAMP(32 + 2 * i);
+      B200Q_TIMER_LAP(2)
+      if (td == 0 && i < 4) B200Q_STAMP(32 + 2 * i);
       const uint32_t p_stage = p_ring + sp * p_group_bytes + ps * PackedStage<FMT>::kBytes;
       const uint32_t a_stage = a_ring + sa * kStageBytesA;
       if (td == 0 && i == 3) B200Q_STAMP(7);
@@ -665,6 +706,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tmem_st_cols<kCols>(a_stage_t + kCols * atm_kq, out);
         }
         if (td == 0 && i == 3) B200Q_STAMP(62);
+        B200Q_TIMER_LAP(3)
         tmem_st_wait();
         if (td == 0 && i == 3) B200Q_STAMP(63);
         tc_fence_before_sync();
@@ -734,7 +776,8 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         mbar_arrive(a_full + 8 * sa);
         if (ps == p.pg - 1 || i == nkb - 1) mbar_arrive(p_empty + 8 * sp);
       }
-      if (td == 0 && i < 12) B200Q_STAMP(33 + 2 * i);
+      if (td == 0 && i < 4) B200Q_STAMP(33 + 2 * i);
+      B200Q_TIMER_LAP(5)
       if (++sa == p.na) {
         sa = 0;
         a_phase ^= 1;
@@ -746,7 +789,10 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           p_phase ^= 1;
         }
       }
+      B200Q_TIMER_LAP(6)
+      B200Q_TIMER_RESET(i == 0)
     }
+    B200Q_TIMER_FLUSH(td == 0)
     if (!ok) flag_failure(abort_p, p.status, 4u);
 
     // ------------------------------------------------------------ epilogue
@@ -855,6 +901,83 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       }
       if (gather) gather_signal_done();
       if (td == 0) B200Q_STAMP(57);
+    } else if (p.cluster_reduce) {
+      // Split-K inside a cluster: the blocks of one tile (cluster = its K splits) each park
+      // their fp32 partial in their own shared memory as [token][128 channels]; after a
+      // cluster barrier block r sums rows r, r + splits, ... over every block's copy (in split
+      // order, so the result equals the workspace path bit for bit) and stores them.  The
+      // rings are idle: every MMA of this block has completed and every copy has landed.
+      const uint32_t park = x_ring;
+      for (int c = 0; c < half_cols; c += 8) {
+        uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        if (acc_ok && nkb > 0) {
+          tmem_ld_x8(tmem_row + (c_begin + c), r);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(park + (c_begin + c + j) * 512 + ch * 4), "r"(r[j])
+                       : "memory");
+      }
+      if (td == 0) B200Q_STAMP(57);
+      cluster_arrive_release();
+      cluster_wait_acquire();
+      {
+        const int n_base = n_tile * kBlockN;
+        const int q4 = td & 31;                           // float4 index inside the row
+        const int nq = n_base + 4 * q4;
+        const int rows = min(p.tok, p.M - m_base);
+        const bool vec4 = (p.N % 4 == 0) && (nq + 4 <= p.N);
+        float sc[4] = {1.0f, 1.0f, 1.0f, 1.0f}, bs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (nq + e < p.N) {
+            if (FMT == FMT_W8)
+              sc[e] = p.scale_is_f32 ? reinterpret_cast<const float*>(p.scales)[nq + e]
+                                     : __half2float(reinterpret_cast<const __half*>(p.scales)[nq + e]);
+            if (p.bias != nullptr) bs[e] = static_cast<float>(static_cast<const T*>(p.bias)[nq + e]);
+          }
+        }
+        constexpr int kMaxCluster = 8;
+        uint32_t peer[kMaxCluster];
+#pragma unroll
+        for (int z = 0; z < kMaxCluster; ++z)
+          peer[z] = map_to_cluster_rank(park + q4 * 16, static_cast<uint32_t>(z < p.splits ? z : 0));
+        for (int r = split + p.splits * (td >> 5); r < rows; r += p.splits * kDequantWarps) {
+          float4 t[kMaxCluster];
+#pragma unroll
+          for (int z = 0; z < kMaxCluster; ++z) {
+            t[z] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (z < p.splits) t[z] = ld_cluster_shared_f4(peer[z] + r * 512);
+          }
+          float4 a = t[0];
+#pragma unroll
+          for (int z = 1; z < kMaxCluster; ++z) {
+            if (z < p.splits) {
+              a.x += t[z].x;
+              a.y += t[z].y;
+              a.z += t[z].z;
+              a.w += t[z].w;
+            }
+          }
+          const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + nq;
+          const float v[4] = {a.x, a.y, a.z, a.w};
+          alignas(8) T o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
+          T* dst = static_cast<T*>(p.y) + off;
+          if (vec4 && reinterpret_cast<uintptr_t>(dst) % 8 == 0) {
+            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (nq + e < p.N) dst[e] = o[e];
+          }
+        }
+      }
+      // no block may leave (and release its shared memory) while a peer still reads it
+      cluster_arrive_release();
+      cluster_wait_acquire();
     } else {
       if (acc_ok && nkb > 0) {
         for (int c = 0; c < half_cols; c += 8) {
@@ -885,8 +1008,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         __threadfence();
         if (gather) gather_wait_ready();
         // Sum the partials of this tile in split order.  Flat mapping: a row of the tile is
-        // 128 channels = 32 float4; one row per warp and 4 passes in flight per thread keep
-        // 4 x splits independent 16-byte loads outstanding (the partials sit in L2).
+        // 128 channels = 32 float4, one row per warp (the partials sit in L2).
         const int n_base = n_tile * kBlockN;
         const int q4 = td & 31;                           // float4 index inside the row
         const int nq = n_base + 4 * q4;
@@ -902,46 +1024,65 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             if (p.bias != nullptr) bs[e] = static_cast<float>(static_cast<const T*>(p.bias)[nq + e]);
           }
         }
-        for (int r0 = td >> 5; r0 < rows; r0 += 4 * kDequantWarps) {
-          float4 acc[4];
+        // kRowsInFlight rows x kSplitBatch splits of independent 16-byte loads are issued before
+        // any is consumed, so a tile costs one L2 round trip per batch, not one per split.
+        constexpr int kRowsInFlight = 2, kSplitBatch = 4;
+        for (int r0 = td >> 5; r0 < rows; r0 += kRowsInFlight * kDequantWarps) {
+          float4 acc[kRowsInFlight];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          for (int z = 0; z < p.splits; ++z) {
-            float4 t[4];
+          for (int u = 0; u < kRowsInFlight; ++u) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          for (int z0 = 0; z0 < p.splits; z0 += kSplitBatch) {
+            float4 t[kSplitBatch][kRowsInFlight];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int r = min(r0 + kDequantWarps * u, rows - 1);
-              const float* src = p.partial + (static_cast<int64_t>(z) * p.M + m_base + r) * p.N + nq;
-              if (vec4) {
-                t[u] = __ldcg(reinterpret_cast<const float4*>(src));
-              } else {
-                t[u].x = (nq + 0 < p.N) ? __ldcg(src + 0) : 0.0f;
-                t[u].y = (nq + 1 < p.N) ? __ldcg(src + 1) : 0.0f;
-                t[u].z = (nq + 2 < p.N) ? __ldcg(src + 2) : 0.0f;
-                t[u].w = (nq + 3 < p.N) ? __ldcg(src + 3) : 0.0f;
+            for (int zz = 0; zz < kSplitBatch; ++zz) {
+#pragma unroll
+              for (int u = 0; u < kRowsInFlight; ++u) {
+                const int r = r0 + kDequantWarps * u;
+                t[zz][u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (z0 + zz < p.splits && r < rows) {
+                  const float* src =
+                      p.partial + (static_cast<int64_t>(z0 + zz) * p.M + m_base + r) * p.N + nq;
+                  if (vec4) {
+                    t[zz][u] = __ldcg(reinterpret_cast<const float4*>(src));
+                  } else {
+                    if (nq + 0 < p.N) t[zz][u].x = __ldcg(src + 0);
+                    if (nq + 1 < p.N) t[zz][u].y = __ldcg(src + 1);
+                    if (nq + 2 < p.N) t[zz][u].z = __ldcg(src + 2);
+                    if (nq + 3 < p.N) t[zz][u].w = __ldcg(src + 3);
+                  }
+                }
               }
             }
+            // absent splits contribute +0.0f, which leaves the running sum unchanged
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              acc[u].x += t[u].x;
-              acc[u].y += t[u].y;
-              acc[u].z += t[u].z;
-              acc[u].w += t[u].w;
+            for (int zz = 0; zz < kSplitBatch; ++zz) {
+#pragma unroll
+              for (int u = 0; u < kRowsInFlight; ++u) {
+                acc[u].x += t[zz][u].x;
+                acc[u].y += t[zz][u].y;
+                acc[u].z += t[zz][u].z;
+                acc[u].w += t[zz][u].w;
+              }
             }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < kRowsInFlight; ++u) {
             const int r = r0 + kDequantWarps * u;
             if (r < rows) {
               const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + col0 + nq;
               const float v[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
-              T o[4];
+              alignas(8) T o[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
+              const bool vec_store = vec4 && ((off * sizeof(T)) % 8 == 0);
               for (int d = 0; d < ndst; ++d) {
+                if (vec_store && reinterpret_cast<uintptr_t>(ydst[d]) % 8 == 0) {
+                  *reinterpret_cast<uint2*>(ydst[d] + off) = *reinterpret_cast<const uint2*>(o);
+                } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (nq + e < p.N) ydst[d][off + e] = o[e];
+                  for (int e = 0; e < 4; ++e)
+                    if (nq + e < p.N) ydst[d][off + e] = o[e];
+                }
               }
             }
           }
@@ -953,6 +1094,14 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   }
 
   if (threadIdx.x == 64) B200Q_STAMP(58);
+  if (p.cluster_reduce && warp < 2) {
+    // the producer and MMA warps only take part in the epilogue's two cluster barriers
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -966,6 +1115,11 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 }
 
 #ifdef B200Q_TRACE
+extern "C" int b200q_trace_clear() {
+  void* sym = nullptr;
+  if (cudaGetSymbolAddress(&sym, g_trace) != cudaSuccess) return 1;
+  return static_cast<int>(cudaMemset(sym, 0, sizeof(g_trace)));
+}
 extern "C" int b200q_trace_read(unsigned long long* host, size_t count) {
   return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, count * sizeof(unsigned long long)));
 }
@@ -1214,6 +1368,31 @@ bool tc_supported(const ForwardArgs& a) {
   return true;
 }
 
+// B200Q_DEBUG_PLAN=1 prints the tiling of every tensor-core launch to stderr.
+static bool debug_plan_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200Q_DEBUG_PLAN");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return on;
+}
+
+static bool cluster_reduce_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200Q_SPLIT_REDUCE");
+    return !(v != nullptr && std::strcmp(v, "workspace") == 0);
+  }();
+  return on;
+}
+
+static bool cluster_reduce_forced() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200Q_SPLIT_REDUCE");
+    return v != nullptr && std::strcmp(v, "cluster") == 0;
+  }();
+  return on;
+}
+
 template <int FMT, typename T, bool ATM, int DW>
 static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   static bool attr_set_dev[64] = {};
@@ -1230,6 +1409,12 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
         set_last_error("cudaFuncSetAttribute", e);
         return B200Q_ERR_CUDA;
       }
+      // ask for the largest shared-memory carve-out so that two blocks fit an SM (also what the
+      // cluster occupancy query assumes)
+      (void)cudaFuncSetAttribute(wq_gemm_tc_kernel<FMT, T, ATM, DW>,
+                                 cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+      (void)cudaGetLastError();
       attr_set = true;
     }
   }
@@ -1298,11 +1483,59 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   cfg.blockDim = dim3(64 + 32 * DW);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = a.stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // Split-K over distributed shared memory: the splits of a tile form a cluster (z direction)
+  // when every cluster of the grid can be resident at once; otherwise, with the fused
+  // all-gather, or on request (B200Q_SPLIT_REDUCE=workspace) the partials go through the
+  // workspace and the last block to arrive sums them.
+  p.cluster_reduce = 0;
+  int resident_clusters = -1;
+  const size_t ring_bytes = static_cast<size_t>(pl.nx) * pl.xg * pl.tok * 256 +
+                            static_cast<size_t>(pl.np) * pl.pg * packed_stage_bytes(a.format);
+  if (ATM && pl.splits > 1 && pl.splits <= 8 && p.g_world == 0 && cluster_reduce_enabled() &&
+      ring_bytes >= static_cast<size_t>(pl.tok) * 512) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = static_cast<unsigned>(pl.splits);
+    cfg.numAttrs = 2;
+    static std::map<std::tuple<int, size_t, int>, int> resident;   // (device, smem, splits) -> clusters
+    static std::mutex resident_mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int clusters = 0;
+    {
+      std::lock_guard<std::mutex> g(resident_mu);
+      const auto key = std::make_tuple(dev, pl.smem_bytes, pl.splits);
+      auto it = resident.find(key);
+      if (it == resident.end()) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, wq_gemm_tc_kernel<FMT, T, ATM, DW>, &cfg) != cudaSuccess) {
+          (void)cudaGetLastError();
+          n = 0;
+        }
+        it = resident.emplace(key, n).first;
+      }
+      clusters = it->second;
+    }
+    resident_clusters = clusters;
+    if (clusters >= pl.n_tiles * pl.m_tiles || (clusters > 0 && cluster_reduce_forced())) {
+      p.cluster_reduce = 1;
+    } else {
+      cfg.numAttrs = 1;
+    }
+  }
+  if (debug_plan_enabled())
+    std::fprintf(stderr,
+                 "b200q plan: fmt %d M %d N %d K %d | tok %d tiles %dx%d splits %d (kb %d/%d) dw %d | "
+                 "rings p %dx%d x %dx%d a %d | smem %zu tmem %d | split reduce: %s (resident clusters %d)\n",
+                 FMT, a.M, a.N, a.K, pl.tok, pl.m_tiles, pl.n_tiles, pl.splits, pl.kb_per_split,
+                 pl.kb_total, DW, pl.np, pl.pg, pl.nx, pl.xg, pl.na, pl.smem_bytes, pl.tmem_cols,
+                 pl.splits == 1 ? "none" : (p.cluster_reduce ? "cluster" : "workspace"), resident_clusters);
   cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T, ATM, DW>, tm_w, tm_x, p);
   if (e != cudaSuccess) {
     set_last_error("cudaLaunchKernelEx", e);
