@@ -23,6 +23,7 @@
 // Reference counterparts: _w4a16_linear_kernel (engine/kernels/w4a16_linear.py:27-74),
 // _w8a16_linear_kernel (engine/kernels/w8a16_linear.py:10-40) and the dense
 // dequantise-then-cuBLAS branch of W4A16Linear (engine/quantization/w4a16.py:158-178).
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -1232,7 +1233,32 @@ static bool use_tmem_operand() {
 static TcPlan make_plan(int format, int M, int N, int K) {
   TcPlan pl{};
   pl.atm = use_tmem_operand();
-  const int mt = (M + 255) / 256;
+  // Token tile: as few tiles as cover M, except that a problem of at most two waves (148
+  // blocks at a time) may take a narrower tile that fills its last wave; with more waves the
+  // widest tile measured best.  Cost model per candidate count of token
+  // tiles: waves x (tile width + fixed set-up/epilogue worth ~40 columns), a tile narrower than
+  // 128 columns being dequantise-bound; a problem under half a wave will be split along K.
+  int mt = (M + 255) / 256;
+  if (pl.atm && M > 256 && mt * ((N + kBlockN - 1) / kBlockN) <= 2 * 148) {
+    const int n_tiles = (N + kBlockN - 1) / kBlockN;
+    const int kb_total = (K + kBlockK - 1) / kBlockK;
+    double best_cost = 0.0;
+    int best_mt = mt;
+    for (int c = mt; c <= mt + 4; ++c) {
+      const int tok_c = ((M + c - 1) / c + 15) / 16 * 16;
+      if (tok_c < 96) break;
+      const int tiles = c * n_tiles;
+      const int waves = (tiles + 147) / 148;
+      int s = 1;
+      if (2 * tiles <= 148) s = std::max(1, std::min(std::min(148 / tiles, kb_total / 8), 8));
+      const double cost = waves * (std::max(tok_c, 128) + 40.0) / s + (s > 1 ? 16.0 : 0.0);
+      if (c == mt || cost < 0.97 * best_cost) {   // more tiles must pay for themselves
+        best_cost = cost;
+        best_mt = c;
+      }
+    }
+    mt = best_mt;
+  }
   int tok = ((M + mt - 1) / mt + 15) / 16 * 16;
   if (tok < 16) tok = 16;
   // Wide tiles own the whole SM: sixteen dequantise warps halve the latency of a dequantise
