@@ -39,6 +39,11 @@ constexpr int kSimtMaxRowsW8 = 1;
 static int run_forward(ForwardArgs& a, int kernel_and_flags) {
   a.static_weights = (kernel_and_flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
   const int kernel = kernel_and_flags & 0xFF;
+  if (a.swiglu) {
+    // the gated-pair epilogue exists in the tensor-core kernel only
+    if (kernel != B200Q_KERNEL_AUTO && kernel != B200Q_KERNEL_TC) return B200Q_ERR_UNSUPPORTED;
+    return launch_forward_tc(a);
+  }
   if (kernel == B200Q_KERNEL_SIMT) return launch_forward_simt(a);
   if (kernel == B200Q_KERNEL_TC) return launch_forward_tc(a);
   if (kernel != B200Q_KERNEL_AUTO) return B200Q_ERR_INVALID;
@@ -135,9 +140,12 @@ int b200q_w8a16_forward(const void* x, int64_t ldx, int act_dtype, const int8_t*
   if (!x || !qweight || !scales || !y) return B200Q_ERR_INVALID;
   if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
   if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
-  if (ldx < K || ldw < K || ldy < N) return B200Q_ERR_INVALID;
+  const bool swiglu = (kernel & B200Q_FLAG_SWIGLU_PAIRS) != 0;
+  if (swiglu && (N & 1)) return B200Q_ERR_INVALID;
+  if (ldx < K || ldw < K || ldy < (swiglu ? N / 2 : N)) return B200Q_ERR_INVALID;
   if (K % 16) return B200Q_ERR_UNSUPPORTED;
   ForwardArgs a{};
+  a.swiglu = swiglu;
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
   a.w = qweight; a.ldw = ldw; a.format = FMT_W8;
   a.scales = scales; a.scale_dtype = scale_dtype; a.zeros = nullptr; a.group = 0;
@@ -162,8 +170,11 @@ int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype, const void* p
   }
   if (group <= 0 || K % group) return B200Q_ERR_INVALID;
   if (group % 32) return B200Q_ERR_UNSUPPORTED;
-  if (ldx < K || ldw < K / 2 || ldy < N) return B200Q_ERR_INVALID;
+  const bool swiglu = (kernel & B200Q_FLAG_SWIGLU_PAIRS) != 0;
+  if (swiglu && (N & 1)) return B200Q_ERR_INVALID;
+  if (ldx < K || ldw < K / 2 || ldy < (swiglu ? N / 2 : N)) return B200Q_ERR_INVALID;
   ForwardArgs a{};
+  a.swiglu = swiglu;
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
   a.w = packed; a.ldw = ldw;
   a.format = layout == B200Q_W4_ASYM_ZP_INT32 ? FMT_W4_ASYM : FMT_W4_REF;
@@ -206,6 +217,7 @@ int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   }
   if (group <= 0 || K % group) return B200Q_ERR_INVALID;
   if (ldx < K || ldw < K / 2) return B200Q_ERR_INVALID;
+  if (flags & B200Q_FLAG_SWIGLU_PAIRS) return B200Q_ERR_INVALID;
   if (int st = check_gather(gather, ldy, N_local)) return st;
   ForwardArgs a{};
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
@@ -230,6 +242,7 @@ int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
   if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
   if (ldx < K || ldw < K) return B200Q_ERR_INVALID;
+  if (flags & B200Q_FLAG_SWIGLU_PAIRS) return B200Q_ERR_INVALID;
   if (int st = check_gather(gather, ldy, N_local)) return st;
   ForwardArgs a{};
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;

@@ -67,6 +67,7 @@ struct TcParams {
   int pg, xg;        // K blocks per weight group / per activation chunk (one TMA each)
   float* partial;    // [splits, M, N] fp32 (split-K only)
   int static_weights;  // weights/scales/bias may be read ahead of the stream order
+  int swiglu;          // rows are (gate, up) pairs: y[m, c] = silu(row 2c) * row 2c+1; N/2 output columns
   // fused all-gather (g_world > 1): every output tile is stored into the [M, ldy] buffer of
   // every rank at column offset g_col0, through peer-mapped pointers
   int g_world, g_rank, g_col0;
@@ -135,6 +136,11 @@ __device__ __forceinline__ __half from_float<__half>(float v) {
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+
+// SiLU-gated product of one (gate, up) pair in fp32: gate * sigmoid(gate) * up.
+__device__ __forceinline__ float swiglu_pair(float gate, float up) {
+  return gate * __frcp_rn(1.0f + __expf(-gate)) * up;
 }
 
 #ifdef B200Q_TRACE
@@ -864,16 +870,28 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const T v = from_float<T>(__uint_as_float(r[j]) * ch_scale + ch_bias);
+            float f = __uint_as_float(r[j]) * ch_scale + ch_bias;
+            bool keep = true;
+            int out_ch = ch, out_n = n;
+            if (p.swiglu) {
+              // neighbouring lanes hold the gate (even row) and up (odd row) of one output
+              const float other = __shfl_xor_sync(0xffffffffu, f, 1);
+              f = swiglu_pair(f, other);
+              keep = (lane & 1) == 0;
+              out_ch = ch >> 1;
+              out_n = n >> 1;
+            }
+            const T v = from_float<T>(f);
             if (vec_out) {
               const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
-              asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + ch * 2),
-                           "h"(bits)
-                           : "memory");
+              if (keep)
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + out_ch * 2),
+                             "h"(bits)
+                             : "memory");
             } else {
               const int m = m_base + c_begin + c + j;
-              if (n < p.N && m < p.M)
-                for (int d = 0; d < ndst; ++d) ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + n] = v;
+              if (keep && n < p.N && m < p.M)
+                for (int d = 0; d < ndst; ++d) ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + out_n] = v;
             }
           }
         }
@@ -882,19 +900,21 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
         if (acc_ok && nkb > 0) {
           const int chunk = td & 15;                       // 8 channels = 16 bytes
-          const int n_c = n_tile * kBlockN + chunk * 8;
+          const int tile_out = p.swiglu ? kBlockN / 2 : kBlockN;   // output columns per tile
+          const int n_out = p.swiglu ? p.N / 2 : p.N;
+          const int n_c = n_tile * tile_out + chunk * 8;
           const int rows = min(p.tok, p.M - m_base);
-          for (int r = td >> 4; r < rows; r += kDequantThreads / 16) {
+          for (int r = td >> 4; r < rows && chunk * 8 < tile_out; r += kDequantThreads / 16) {
             const uint4 v = ld_shared_v4(stage + r * 256 + chunk * 16);
             const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + col0 + n_c;
             for (int d = 0; d < ndst; ++d) {
               T* dst = ydst[d] + off;
-              if (n_c + 8 <= p.N) {
+              if (n_c + 8 <= n_out) {
                 *reinterpret_cast<uint4*>(dst) = v;
               } else {
                 const T* e = reinterpret_cast<const T*>(&v);
                 for (int k = 0; k < 8; ++k)
-                  if (n_c + k < p.N) dst[k] = e[k];
+                  if (n_c + k < n_out) dst[k] = e[k];
               }
             }
           }
@@ -963,6 +983,15 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
           const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + nq;
           const float v[4] = {a.x, a.y, a.z, a.w};
+          if (p.swiglu) {
+            // channels nq..nq+3 are two (gate, up) pairs -> output columns nq/2, nq/2 + 1
+            T* dst2 = static_cast<T*>(p.y) + static_cast<int64_t>(m_base + r) * p.ldy + (nq >> 1);
+            if (nq + 1 < p.N)
+              dst2[0] = from_float<T>(swiglu_pair(v[0] * sc[0] + bs[0], v[1] * sc[1] + bs[1]));
+            if (nq + 3 < p.N)
+              dst2[1] = from_float<T>(swiglu_pair(v[2] * sc[2] + bs[2], v[3] * sc[3] + bs[3]));
+            continue;
+          }
           alignas(8) T o[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
@@ -1072,6 +1101,17 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             if (r < rows) {
               const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + col0 + nq;
               const float v[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+              if (p.swiglu) {
+                // channels nq..nq+3 are two (gate, up) pairs -> output columns nq/2, nq/2 + 1
+                const int64_t off2 = static_cast<int64_t>(m_base + r) * p.ldy + col0 + (nq >> 1);
+                const T o0 = from_float<T>(swiglu_pair(v[0] * sc[0] + bs[0], v[1] * sc[1] + bs[1]));
+                const T o1 = from_float<T>(swiglu_pair(v[2] * sc[2] + bs[2], v[3] * sc[3] + bs[3]));
+                for (int d = 0; d < ndst; ++d) {
+                  if (nq + 1 < p.N) ydst[d][off2] = o0;
+                  if (nq + 3 < p.N) ydst[d][off2 + 1] = o1;
+                }
+                continue;
+              }
               alignas(8) T o[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
@@ -1486,6 +1526,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.pg = pl.pg;
   p.xg = pl.xg;
   p.static_weights = a.static_weights ? 1 : 0;
+  p.swiglu = a.swiglu ? 1 : 0;
   p.g_world = 0;
   if (a.gather != nullptr && a.gather->world > 1) {
     p.g_world = a.gather->world;

@@ -18,7 +18,8 @@ from .w4a16_format import (  # noqa: F401  (re-exported like the reference modul
 _KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERNEL_TC}
 
 
-def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, static_weights=False):
+def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, static_weights=False,
+             swiglu_pairs=False):
     _lib.require_cuda(inputs, "inputs")
     m, k = inputs.shape
     n = packed.shape[0]
@@ -39,9 +40,11 @@ def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, sta
     if bias is not None:
         b = bias if (bias.dtype is inputs.dtype and bias.is_contiguous()) \
             else bias.to(inputs.dtype).contiguous()
-    out = torch.empty((m, n), dtype=inputs.dtype, device=inputs.device)
+    out = torch.empty((m, n // 2 if swiglu_pairs else n), dtype=inputs.dtype, device=inputs.device)
     if m == 0 or n == 0:
         return out
+    flags = (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0) \
+        | (_lib.FLAG_SWIGLU_PAIRS if swiglu_pairs else 0)
     need = _lib.workspace_bytes(4, m, n, k)
     ws = _lib.workspace_for(inputs.device, need)
     layout = _lib.W4_REF_SPLIT_HALF_SYM if zeros is None else _lib.W4_ASYM_ZP_INT32
@@ -52,7 +55,7 @@ def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, sta
             s.data_ptr(), None if z is None else z.data_ptr(), group_size,
             None if b is None else b.data_ptr(),
             out.data_ptr(), out.stride(0), m, n, k,
-            ws.data_ptr(), ws.numel(), kernel | (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0),
+            ws.data_ptr(), ws.numel(), kernel | flags,
             _lib.stream_ptr(inputs.device)), where)
     return out
 
@@ -61,14 +64,16 @@ def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tenso
                  bias: torch.Tensor | None = None, *, group_size: int = GROUP_SIZE,
                  block_m: int = 16, block_n: int = 64, num_warps: int = 4,
                  kernel: str = "auto", zeros: torch.Tensor | None = None,
-                 static_weights: bool = False) -> torch.Tensor:
+                 static_weights: bool = False, swiglu_pairs: bool = False) -> torch.Tensor:
     """``inputs [M, K]`` x dequantised ``packed/scales`` -> ``[M, N]`` in ``inputs.dtype``.
 
     Reference: ``w4a16_linear`` (engine/kernels/w4a16_linear.py:77-117).  With ``zeros``
     the weights are the asymmetric int32 layout (``packed`` is ``[N, K//8] int32``).
     ``static_weights=True`` promises that packed/scales/zeros/bias were not written by the
     kernel just before this call in the stream (module buffers): the kernel may then read
-    them while that kernel is still finishing.
+    them while that kernel is still finishing.  ``swiglu_pairs=True``: the rows are
+    interleaved (gate, up) pairs and the result is ``silu(gate) * up``, ``[M, N // 2]``
+    (see ``kernels/swiglu.py``).
     """
     asym = zeros is not None
     want = torch.int32 if asym else torch.uint8
@@ -88,8 +93,10 @@ def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tenso
         raise ValueError("bias must have shape [N]")
     if block_m < 16 or block_n < 16:
         raise ValueError("tl.dot requires tiles of at least 16")
+    if swiglu_pairs and n % 2:
+        raise ValueError("gate/up pairs need an even number of weight rows")
     return _forward(inputs, packed, scales, zeros, bias, group_size, _KERNELS[kernel], "w4a16_linear",
-                    static_weights)
+                    static_weights, swiglu_pairs)
 
 
 def w4a16_gemv(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,

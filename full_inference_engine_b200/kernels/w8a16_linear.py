@@ -45,12 +45,12 @@ def quantize_weight_per_channel_fp32_scales(weight: torch.Tensor) -> tuple[torch
 
 def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
                  bias: torch.Tensor | None = None, *, kernel: str = "auto",
-                 static_weights: bool = False) -> torch.Tensor:
+                 static_weights: bool = False, swiglu_pairs: bool = False) -> torch.Tensor:
     """W8A16 linear for 2-D activations (engine/kernels/w8a16_linear.py:50-69).
 
     The integer weights enter the multiply unscaled (they are exact in fp16 and bf16);
     the per-channel scale and the bias are applied to the fp32 accumulator.
-    ``static_weights``: see ``w4a16_linear``.
+    ``static_weights`` and ``swiglu_pairs``: see ``w4a16_linear``.
     """
     if inputs.ndim != 2 or qweight.ndim != 2 or qweight.dtype is not torch.int8:
         raise ValueError("inputs must be 2D and qweight must be 2D INT8")
@@ -64,6 +64,8 @@ def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tens
         raise ValueError(f"kernel must be auto, gemv or dot; got {kernel!r}")
     if inputs.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("inputs must be fp16 or bf16")
+    if swiglu_pairs and n % 2:
+        raise ValueError("gate/up pairs need an even number of weight rows")
     _lib.require_cuda(inputs, "inputs")
     x = inputs if (inputs.stride(1) == 1 and inputs.stride(0) % 8 == 0
                    and inputs.data_ptr() % 16 == 0) else inputs.contiguous()
@@ -75,9 +77,11 @@ def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tens
     if bias is not None:
         b = bias if (bias.dtype is inputs.dtype and bias.is_contiguous()) \
             else bias.to(inputs.dtype).contiguous()
-    out = torch.empty((m, n), dtype=inputs.dtype, device=inputs.device)
+    out = torch.empty((m, n // 2 if swiglu_pairs else n), dtype=inputs.dtype, device=inputs.device)
     if m == 0 or n == 0:
         return out
+    flags = (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0) \
+        | (_lib.FLAG_SWIGLU_PAIRS if swiglu_pairs else 0)
     ws = _lib.workspace_for(inputs.device, _lib.workspace_bytes(8, m, n, k))
     with torch.cuda.device(inputs.device):
         _lib.check(_lib.library().b200q_w8a16_forward(
@@ -86,7 +90,7 @@ def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tens
             None if b is None else b.data_ptr(),
             out.data_ptr(), out.stride(0), m, n, k,
             ws.data_ptr(), ws.numel(),
-            _KERNELS[kernel] | (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0),
+            _KERNELS[kernel] | flags,
             _lib.stream_ptr(inputs.device)),
             "w8a16_linear")
     return out

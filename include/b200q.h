@@ -71,6 +71,17 @@ typedef enum b200q_kernel {
  * outputs and the workspace always stay in stream order.  Without the flag
  * everything stays in stream order.                                            */
 #define B200Q_FLAG_STATIC_WEIGHTS 0x100
+/* SWIGLU_PAIRS: the weight rows are (gate, up) pairs of a gated feed-forward, interleaved:
+ * row 2c is gate channel c and row 2c+1 is up channel c (scales, zero-points and bias
+ * interleaved the same way).  The call then writes N/2 columns,
+ *   y[m, c] = silu(acc[m, 2c]) * acc[m, 2c+1]       (acc includes the scale and bias),
+ * evaluated in fp32 and rounded once to the activation dtype; ldy >= N/2, N even.  It fuses
+ * the reference's gate_proj + up_proj + silu(gate) * up (engine/kernels/swiglu.py:65-83,
+ * 86-107: FusedGateUpProjection followed by triton_swiglu), which the reference can only
+ * build from fp16 `.weight`s, not from quantized modules.  Tensor-core kernel only
+ * (B200Q_ERR_UNSUPPORTED with B200Q_KERNEL_SIMT or an unsupported geometry); not accepted
+ * by the *_forward_gather entry points.                                                   */
+#define B200Q_FLAG_SWIGLU_PAIRS 0x200
 
 /* W8 quantizer flavours */
 typedef enum b200q_w8_mode {

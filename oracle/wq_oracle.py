@@ -156,6 +156,18 @@ def linear_fp32(x: np.ndarray, w_deq: np.ndarray, bias: np.ndarray | None = None
     return y
 
 
+def swiglu_fp32(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """``silu(gate) * up`` in fp32: the arithmetic of the reference's SwiGLU kernel
+    (engine/kernels/swiglu.py:22-26, ``gate * sigmoid(gate) * up`` on fp32 promotions)."""
+    g = gate.astype(np.float32)
+    return g * (np.float32(1.0) / (np.float32(1.0) + np.exp(-g))) * up.astype(np.float32)
+
+
+def interleave_rows(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """Rows gate[0], up[0], gate[1], up[1], ... (the fused gate/up weight order)."""
+    return np.stack((gate, up), axis=1).reshape((2 * gate.shape[0],) + gate.shape[1:])
+
+
 def within_tolerance(actual: np.ndarray, truth: np.ndarray, rel: float = 1e-2) -> tuple[bool, float]:
     """The acceptance bar: max|actual - truth| <= rel * max|truth|.  Returns (ok, ratio)."""
     denom = float(np.abs(truth).max())
