@@ -52,9 +52,11 @@ NCU_TRAFFIC_BYTES: dict[str, float] = {
 
 
 class Case:
-    def __init__(self, name, fmt, m, k, n, dtype, outliers=False):
+    def __init__(self, name, fmt, m, k, n, dtype, outliers=False, swiglu=False):
         self.name, self.fmt, self.m, self.k, self.n = name, fmt, m, k, n
         self.dtype, self.outliers = dtype, outliers
+        # n rows are interleaved (gate, up) pairs and the output is silu(gate) * up, n / 2 wide
+        self.swiglu = swiglu
 
     @property
     def key(self):
@@ -75,7 +77,8 @@ class Case:
     @property
     def bytes(self):
         """Algorithmic bytes: every weight byte once, activations in, outputs out."""
-        return float(self.weight_bytes() + 2 * self.m * self.k + 2 * self.m * self.n)
+        n_out = self.n // 2 if self.swiglu else self.n
+        return float(self.weight_bytes() + 2 * self.m * self.k + 2 * self.m * n_out)
 
 
 def build_cases(workload: str, layout: str) -> list[Case]:
@@ -91,6 +94,12 @@ def build_cases(workload: str, layout: str) -> list[Case]:
                 for name in ("q", "kv", "o", "gate_up", "down") for m in (1, 16, 64, 512)]
     if workload == "c1":
         return [Case("gate_0p6b", "w8", 8, 1024, 3072, torch.float16)]
+    if workload == "mlp":
+        # beyond the reference: gate_proj + up_proj + silu(gate) * up of a Qwen3-8B feed-forward
+        # as ONE launch over interleaved quantized rows (2 x 12288 rows of K = 4096)
+        k, n = SHAPES_8B["gate_up"]
+        return [Case("gate_up_swiglu", w4, m, k, 2 * n, torch.float16, swiglu=True)
+                for m in (1, 16, 64, 256, 1024)]
     if workload == "c3":
         # one mixed step of a Qwen3-0.6B-shaped model: 16 decode rows + one 128-token chunk
         shapes = {"q": (1024, 2048), "k": (1024, 1024), "v": (1024, 1024), "o": (2048, 1024),
@@ -219,11 +228,22 @@ def make_weight_sets(cases: list[Case], copies: int, device, rank: int = 0, worl
 def forward(case: Case, x: torch.Tensor, weights: tuple) -> torch.Tensor:
     from full_inference_engine_b200.kernels import w4a16_linear, w8a16_linear
 
+    pairs = case.swiglu
     if case.fmt == "w8":
-        return w8a16_linear.w8a16_linear(x, weights[0], weights[1], static_weights=True)
+        return w8a16_linear.w8a16_linear(x, weights[0], weights[1], static_weights=True, swiglu_pairs=pairs)
     if case.fmt == "w4_ref":
-        return w4a16_linear.w4a16_linear(x, weights[0], weights[1], static_weights=True)
-    return w4a16_linear.w4a16_linear(x, weights[0], weights[1], zeros=weights[2], static_weights=True)
+        return w4a16_linear.w4a16_linear(x, weights[0], weights[1], static_weights=True, swiglu_pairs=pairs)
+    return w4a16_linear.w4a16_linear(x, weights[0], weights[1], zeros=weights[2], static_weights=True,
+                                     swiglu_pairs=pairs)
+
+
+def unfused_forward(case: Case, x: torch.Tensor, halves: tuple) -> torch.Tensor:
+    """What the fused gate/up + SwiGLU launch replaces: two projections and an elementwise
+    kernel (the reference's route, engine/kernels/swiglu.py:65-83 without its fp16 fusion)."""
+    from full_inference_engine_b200.kernels import swiglu
+
+    plain = Case(case.name, case.fmt, case.m, case.k, case.n // 2, case.dtype)
+    return swiglu.swiglu_reference(forward(plain, x, halves[0]), forward(plain, x, halves[1]))
 
 
 # --------------------------------------------------------------------------- CPU path
@@ -257,7 +277,9 @@ def cpu_step(cases, weights, acts, limit=None):
         if limit is not None and i not in limit:
             continue
         w = weights[(case.fmt, case.name)]
-        if case.fmt == "w8":
+        if case.swiglu:
+            cpu_path.gate_up_swiglu_forward(acts[i], w[0], w[1], int8=case.fmt == "w8")
+        elif case.fmt == "w8":
             cpu_path.int8linear_forward(acts[i], w[0], w[1])
         else:
             cpu_path.w4a16_dense_forward(acts[i], w[0], w[1])
@@ -337,6 +359,10 @@ def config_dict(args, cases, rotation):
                            "gate/up and down",
                      "c4": "config 4: W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, M in {1,16,64,512}",
                      "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16",
+                     "mlp": "beyond the reference: INT4 g128 gate_proj + up_proj + silu(gate) * up of a "
+                            "Qwen3-8B feed-forward (K=4096, 2 x 12288 interleaved rows) in one launch, "
+                            "M in {1,16,64,256,1024}, fp16; per_case carries the two-projections-plus-"
+                            "elementwise time beside it",
                      "c3": "config 3: 28 x 7 random-init Qwen3-0.6B W8A16 projections, one mixed "
                            "step of M=144 rows (16 decode + 128 prefill), fp16, one CUDA graph"}[args.workload],
         "layout": {"asym": "asymmetric int32 x8 nibbles + fp16 scale and zero-point",
@@ -388,11 +414,11 @@ def run_b200(args, cases):
             print(f"# rank {rank}: {msg}", file=sys.stderr, flush=True)
 
     pk = peaks()
-    copies = {"c1": 48, "c2": 10, "c3": 1, "c4": 4, "c5": 6}[args.workload]
+    copies = {"c1": 48, "c2": 10, "c3": 1, "c4": 4, "c5": 6, "mlp": 6}[args.workload]
     weight_sets = make_weight_sets(cases, copies, device, rank, world)
     acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
     # per-rank view of each case
-    local_cases = [Case(c.name, c.fmt, c.m, c.k, c.n // world, c.dtype, c.outliers) for c in cases]
+    local_cases = [Case(c.name, c.fmt, c.m, c.k, c.n // world, c.dtype, c.outliers, c.swiglu) for c in cases]
     gathered = [torch.empty(world, c.m, c.n // world, dtype=c.dtype, device=device) if world > 1 else None
                 for c in cases]
     # fused all-gather: full [M, N] outputs in symmetric memory, written by every rank's epilogue
@@ -450,7 +476,8 @@ def run_b200(args, cases):
 
     # ---- end to end (measured before any graph holds NCCL work): pinned host activations in, host results out, through the public API
     host_x = [torch.empty(c.m, c.k, dtype=c.dtype).pin_memory().copy_(acts[i].cpu()) for i, c in enumerate(cases)]
-    host_y = [torch.empty(c.m, c.n if fused_out is not None else c.n // world, dtype=c.dtype).pin_memory()
+    host_y = [torch.empty(c.m, (c.n if fused_out is not None else c.n // world) // (2 if c.swiglu else 1),
+                          dtype=c.dtype).pin_memory()
               for c in cases]
     dev_x = [torch.empty_like(a) for a in acts]
 
@@ -635,6 +662,28 @@ def run_b200(args, cases):
         entry.update(roofline_entry(case, sec, pk))
         entry["frac_of_nominal"] = round(
             max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
+        if case.swiglu:
+            # the same work as two projections + an elementwise kernel, same protocol
+            halves = [tuple(tuple(t[part::2].contiguous() for t in w) for part in (0, 1)) for w in sets]
+            unfused_forward(case, acts[i], halves[0])
+            torch.cuda.synchronize()
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2):
+                for h in halves:
+                    unfused_forward(case, acts[i], h)
+            for _ in range(3):
+                g2.replay()
+            torch.cuda.synchronize()
+            times2 = []
+            for _ in range(7):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                g2.replay()
+                e.record()
+                torch.cuda.synchronize()
+                times2.append(s.elapsed_time(e) / reps)
+            entry["unfused_us"] = round(statistics.median(times2) * 1e3, 2)
+            del g2, halves
         per_case.append(entry)
         del g
     clocks = sampler.stop()
@@ -717,7 +766,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "mlp"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
@@ -732,6 +781,8 @@ def main():
         cases = [c for c in cases if any(c.key.endswith(w) or w in c.key for w in wanted)]
         if not cases:
             raise SystemExit("--cases matched nothing")
+    if args.workload == "mlp" and args.gpus > 1:
+        raise SystemExit("the mlp workload is single-GPU (the gather entry points do not take gate/up pairs)")
     if args.profile:
         run_profile(args, cases)
         return

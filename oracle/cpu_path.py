@@ -91,3 +91,17 @@ def w4a16_asym_dense_forward(x: torch.Tensor, packed: torch.Tensor, scales: torc
                                 in_features, group_size).to(rows.dtype)
         out[:, start:stop] = F.linear(rows, weight)
     return out.reshape(*x.shape[:-1], out_features)
+
+
+def gate_up_swiglu_forward(x: torch.Tensor, weights_pairs: torch.Tensor, scales_pairs: torch.Tensor,
+                           *, int8: bool = False, group_size: int = 128) -> torch.Tensor:
+    """The reference's unfused feed-forward front half on CPU over interleaved (gate, up) rows:
+    two dequantise-then-``F.linear`` projections (engine/quantization/w4a16.py:158-178 or
+    engine/quantization/int8.py:30-33) and ``silu(gate) * up`` evaluated in fp32 and stored in
+    the activation dtype (engine/kernels/swiglu.py:22-26)."""
+    halves = []
+    for part in (0, 1):
+        w, s = weights_pairs[part::2].contiguous(), scales_pairs[part::2].contiguous()
+        halves.append(int8linear_forward(x, w, s) if int8 else w4a16_dense_forward(x, w, s, None, group_size))
+    g = halves[0].float()
+    return (g * torch.sigmoid(g) * halves[1].float()).to(x.dtype)
