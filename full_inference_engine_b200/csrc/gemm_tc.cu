@@ -868,30 +868,42 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           uint32_t r[8];
           tmem_ld_x8(tmem_row + (c_begin + c), r);
           tmem_ld_wait();
+          if (!p.swiglu) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float f = __uint_as_float(r[j]) * ch_scale + ch_bias;
-            bool keep = true;
-            int out_ch = ch, out_n = n;
-            if (p.swiglu) {
-              // neighbouring lanes hold the gate (even row) and up (odd row) of one output
-              const float other = __shfl_xor_sync(0xffffffffu, f, 1);
-              f = swiglu_pair(f, other);
-              keep = (lane & 1) == 0;
-              out_ch = ch >> 1;
-              out_n = n >> 1;
-            }
-            const T v = from_float<T>(f);
-            if (vec_out) {
-              const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
-              if (keep)
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + out_ch * 2),
+            for (int j = 0; j < 8; ++j) {
+              const T v = from_float<T>(__uint_as_float(r[j]) * ch_scale + ch_bias);
+              if (vec_out) {
+                const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + ch * 2),
                              "h"(bits)
                              : "memory");
-            } else {
-              const int m = m_base + c_begin + c + j;
-              if (keep && n < p.N && m < p.M)
-                for (int d = 0; d < ndst; ++d) ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + out_n] = v;
+              } else {
+                const int m = m_base + c_begin + c + j;
+                if (n < p.N && m < p.M)
+                  for (int d = 0; d < ndst; ++d) ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + n] = v;
+              }
+            }
+          } else {
+            // gated pairs: neighbouring lanes hold the gate (even row) and the up (odd row) of
+            // one output channel; the even lane keeps silu(gate) * up
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float f = __uint_as_float(r[j]) * ch_scale + ch_bias;
+              const float other = __shfl_xor_sync(0xffffffffu, f, 1);
+              const T v = from_float<T>(swiglu_pair(f, other));
+              if ((lane & 1) == 0) {
+                if (vec_out) {
+                  const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
+                  asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + (ch >> 1) * 2),
+                               "h"(bits)
+                               : "memory");
+                } else {
+                  const int m = m_base + c_begin + c + j;
+                  if (n < p.N && m < p.M)
+                    for (int d = 0; d < ndst; ++d)
+                      ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + (n >> 1)] = v;
+                }
+              }
             }
           }
         }
