@@ -68,6 +68,7 @@ struct TcParams {
   float* partial;    // [splits, M, N] fp32 (split-K only)
   int static_weights;  // weights/scales/bias may be read ahead of the stream order
   int swiglu;          // rows are (gate, up) pairs: y[m, c] = silu(row 2c) * row 2c+1; N/2 output columns
+  int y_tma;           // finished tiles leave shared memory through one TMA store (tm_y is valid)
   // fused all-gather (g_world > 1): every output tile is stored into the [M, ldy] buffer of
   // every rank at column offset g_col0, through peer-mapped pointers
   int g_world, g_rank, g_col0;
@@ -138,6 +139,18 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
 }
 
+// Two floats -> one 32-bit word of two T (first in the low half), one packed conversion.
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  return as_u32(__floats2half2_rn(lo, hi));
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  return as_u32(__floats2bfloat162_rn(lo, hi));
+}
+
 // SiLU-gated product of one (gate, up) pair in fp32: gate * sigmoid(gate) * up.
 __device__ __forceinline__ float swiglu_pair(float gate, float up) {
   return gate * __frcp_rn(1.0f + __expf(-gate)) * up;
@@ -171,6 +184,10 @@ __device__ __forceinline__ unsigned long long global_ns() {
   if (on) {                                                                                  \
     for (int k = 0; k < 8; ++k) g_trace[(trace_cta & 1023) * 64 + 40 + k] = tmr_acc[k];      \
   }
+#define B200Q_TIMER_FLUSH_EPI(on)                                                            \
+  if (on) {                                                                                  \
+    for (int k = 0; k < 4; ++k) g_trace[(trace_cta & 1023) * 64 + 52 + k] = tmr_acc[k];      \
+  }
 #define B200Q_TIMER_FLUSH_MMA                                                                \
   {                                                                                          \
     for (int k = 0; k < 4; ++k) g_trace[(trace_cta & 1023) * 64 + 48 + k] = tmr_acc[k];      \
@@ -186,6 +203,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 #define B200Q_TIMER_LAP(k)
 #define B200Q_TIMER_RESET(on)
 #define B200Q_TIMER_FLUSH(on)
+#define B200Q_TIMER_FLUSH_EPI(on)
 #define B200Q_TIMER_FLUSH_MMA
 #endif
 
@@ -341,7 +359,7 @@ __device__ __forceinline__ void tmem_st_cols<32>(uint32_t taddr, const uint32_t 
 template <int FMT, typename T, bool ATM, int DW>
 __global__ void __launch_bounds__(64 + 32 * DW, (ATM && DW == 8) ? 2 : 1)
 wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                  const TcParams p) {
+                  const __grid_constant__ CUtensorMap tm_y, const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled operand tiles
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -403,6 +421,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       *last_p = 0;
       tma_prefetch_desc(&tm_w);
       tma_prefetch_desc(&tm_x);
+      if (p.y_tma) tma_prefetch_desc(&tm_y);
     }
     mbar_fence_init();
   }
@@ -857,67 +876,96 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
     if (p.splits == 1) {
       if (gather) gather_wait_ready();
-      // accumulators -> output dtype -> shared memory as [token][128 channels], then
-      // 16-byte row-contiguous stores (the operand rings are idle by now)
+      // accumulators -> output dtype -> shared memory as dense rows [token][tile_out channels]
+      // (the operand rings are idle by now), then either ONE TMA store of the whole tile
+      // (rows/columns beyond M/N are clipped by the tensor map) or 16-byte row stores
       const uint32_t stage = x_ring;
+      const int tile_out = p.swiglu ? kBlockN / 2 : kBlockN;   // output columns per tile
+      const int pitch = 2 * tile_out;                          // bytes per staged row
       const bool vec_out = (p.ldy % 8 == 0) && (col0 % 8 == 0) &&
                            (reinterpret_cast<uintptr_t>(ydst[0]) % 16 == 0) &&
                            (p.nx * x_chunk_bytes >= p.tok * 256);
+      const bool tma_out = vec_out && p.y_tma != 0;
+      B200Q_TIMER_DECL
       if (acc_ok && nkb > 0) {
         for (int c = 0; c < half_cols; c += 8) {
           uint32_t r[8];
+          B200Q_TIMER_LAP(1)
           tmem_ld_x8(tmem_row + (c_begin + c), r);
           tmem_ld_wait();
-          if (!p.swiglu) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const T v = from_float<T>(__uint_as_float(r[j]) * ch_scale + ch_bias);
-              if (vec_out) {
-                const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + ch * 2),
-                             "h"(bits)
+          B200Q_TIMER_LAP(0)
+          // Two columns per conversion instruction (the packed float -> half2 / bfloat162 form;
+          // the scalar conversion is several times slower).  The plain and the gated-pair
+          // forms are separate loops: the plain one is the prefill hot path.
+          auto put2 = [&](int col, int out_ch, int out_n, bool keep, uint32_t two) {
+            if (vec_out) {
+              const uint32_t at = stage + col * pitch + out_ch * 2;
+              if (keep) {
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(at), "h"(static_cast<unsigned short>(two & 0xFFFFu))
                              : "memory");
-              } else {
-                const int m = m_base + c_begin + c + j;
-                if (n < p.N && m < p.M)
-                  for (int d = 0; d < ndst; ++d) ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + n] = v;
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(at + pitch), "h"(static_cast<unsigned short>(two >> 16))
+                             : "memory");
+              }
+            } else if (keep && n < p.N) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int m = m_base + col + h;
+                const unsigned short bits = static_cast<unsigned short>(h ? (two >> 16) : (two & 0xFFFFu));
+                if (m < p.M)
+                  for (int d = 0; d < ndst; ++d)
+                    reinterpret_cast<unsigned short*>(ydst[d])[static_cast<int64_t>(m) * p.ldy + col0 + out_n] = bits;
               }
             }
+          };
+          if (!p.swiglu && vec_out) {
+            // the prefill hot path, spelled out: constant row pitch, no predicates
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              const uint32_t two = pack_pair<T>(__uint_as_float(r[j]) * ch_scale + ch_bias,
+                                                __uint_as_float(r[j + 1]) * ch_scale + ch_bias);
+              const uint32_t at = stage + (c_begin + c + j) * 256 + ch * 2;
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(at), "h"(static_cast<unsigned short>(two & 0xFFFFu))
+                           : "memory");
+              asm volatile("st.shared.u16 [%0], %1;" ::"r"(at + 256), "h"(static_cast<unsigned short>(two >> 16))
+                           : "memory");
+            }
+          } else if (!p.swiglu) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2)
+              put2(c_begin + c + j, ch, n, true,
+                   pack_pair<T>(__uint_as_float(r[j]) * ch_scale + ch_bias,
+                                __uint_as_float(r[j + 1]) * ch_scale + ch_bias));
           } else {
             // gated pairs: neighbouring lanes hold the gate (even row) and the up (odd row) of
             // one output channel; the even lane keeps silu(gate) * up
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float f = __uint_as_float(r[j]) * ch_scale + ch_bias;
-              const float other = __shfl_xor_sync(0xffffffffu, f, 1);
-              const T v = from_float<T>(swiglu_pair(f, other));
-              if ((lane & 1) == 0) {
-                if (vec_out) {
-                  const unsigned short bits = *reinterpret_cast<const unsigned short*>(&v);
-                  asm volatile("st.shared.u16 [%0], %1;" ::"r"(stage + (c_begin + c + j) * 256 + (ch >> 1) * 2),
-                               "h"(bits)
-                               : "memory");
-                } else {
-                  const int m = m_base + c_begin + c + j;
-                  if (n < p.N && m < p.M)
-                    for (int d = 0; d < ndst; ++d)
-                      ydst[d][static_cast<int64_t>(m) * p.ldy + col0 + (n >> 1)] = v;
-                }
-              }
+            for (int j = 0; j < 8; j += 2) {
+              const float f0 = __uint_as_float(r[j]) * ch_scale + ch_bias;
+              const float f1 = __uint_as_float(r[j + 1]) * ch_scale + ch_bias;
+              const float g0 = swiglu_pair(f0, __shfl_xor_sync(0xffffffffu, f0, 1));
+              const float g1 = swiglu_pair(f1, __shfl_xor_sync(0xffffffffu, f1, 1));
+              put2(c_begin + c + j, ch >> 1, n >> 1, (lane & 1) == 0, pack_pair<T>(g0, g1));
             }
           }
         }
       }
+      B200Q_TIMER_LAP(1)
       if (vec_out) {
+        if (tma_out) fence_proxy_async_smem();   // staged rows -> visible to the TMA engine
         asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
-        if (acc_ok && nkb > 0) {
+        B200Q_TIMER_LAP(2)
+        if (tma_out) {
+          if (td == 0 && acc_ok && nkb > 0) {
+            tma_store_3d(&tm_y, stage, n_tile * tile_out, m_base, 0);
+            tma_store_commit_and_wait_read();
+          }
+        } else if (acc_ok && nkb > 0) {
           const int chunk = td & 15;                       // 8 channels = 16 bytes
-          const int tile_out = p.swiglu ? kBlockN / 2 : kBlockN;   // output columns per tile
           const int n_out = p.swiglu ? p.N / 2 : p.N;
           const int n_c = n_tile * tile_out + chunk * 8;
           const int rows = min(p.tok, p.M - m_base);
           for (int r = td >> 4; r < rows && chunk * 8 < tile_out; r += kDequantThreads / 16) {
-            const uint4 v = ld_shared_v4(stage + r * 256 + chunk * 16);
+            const uint4 v = ld_shared_v4(stage + r * pitch + chunk * 16);
             const int64_t off = static_cast<int64_t>(m_base + r) * p.ldy + col0 + n_c;
             for (int d = 0; d < ndst; ++d) {
               T* dst = ydst[d] + off;
@@ -932,6 +980,8 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           }
         }
       }
+      B200Q_TIMER_LAP(3)
+      B200Q_TIMER_FLUSH_EPI(td == 0)
       if (gather) gather_signal_done();
       if (td == 0) B200Q_STAMP(57);
     } else if (p.cluster_reduce) {
@@ -1455,6 +1505,16 @@ static bool debug_plan_enabled() {
   return on;
 }
 
+// B200Q_TILE_STORE=rows keeps the per-thread 16-byte row stores of a finished tile instead of
+// the TMA store (for comparison).
+static bool tma_store_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200Q_TILE_STORE");
+    return !(v != nullptr && std::strcmp(v, "rows") == 0);
+  }();
+  return on;
+}
+
 static bool cluster_reduce_enabled() {
   static const bool on = [] {
     const char* v = std::getenv("B200Q_SPLIT_REDUCE");
@@ -1514,7 +1574,26 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
                       static_cast<uint32_t>(2 * pl.xg), CU_TENSOR_MAP_SWIZZLE_128B))
     return B200Q_ERR_CUDA;
 
+  // Output as {N_out, M, 1}: a finished tile [tok rows x tile_out columns] leaves shared memory
+  // through one TMA store.  Needs 16-byte aligned rows; the fused all-gather (peer pointers,
+  // one copy per rank) and split-K keep their own store paths.
+  CUtensorMap tm_y{};
+  const bool gathering = a.gather != nullptr && a.gather->world > 1;
+  const int n_out = a.swiglu ? a.N / 2 : a.N;
+  const bool y_tma = ATM && !gathering && pl.splits == 1 && (a.ldy % 8 == 0) &&
+                     (reinterpret_cast<uintptr_t>(a.y) % 16 == 0) && tma_store_enabled();
+  if (y_tma) {
+    const CUtensorMapDataType ydt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (!get_tensor_map(&tm_y, a.y, ydt, static_cast<uint64_t>(n_out), static_cast<uint64_t>(a.M), 1,
+                        static_cast<uint64_t>(a.ldy) * 2, static_cast<uint64_t>(a.ldy) * 2 * a.M,
+                        static_cast<uint32_t>(a.swiglu ? kBlockN / 2 : kBlockN),
+                        static_cast<uint32_t>(pl.tok), 1, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return B200Q_ERR_CUDA;
+  }
+
   TcParams p{};
+  p.y_tma = y_tma ? 1 : 0;
   p.scales = a.scales;
   p.scale_is_f32 = a.scale_dtype == B200Q_F32;
   p.zeros = static_cast<const __half*>(a.zeros);
@@ -1615,7 +1694,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
                  FMT, a.M, a.N, a.K, pl.tok, pl.m_tiles, pl.n_tiles, pl.splits, pl.kb_per_split,
                  pl.kb_total, DW, pl.np, pl.pg, pl.nx, pl.xg, pl.na, pl.smem_bytes, pl.tmem_cols,
                  pl.splits == 1 ? "none" : (p.cluster_reduce ? "cluster" : "workspace"), resident_clusters);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T, ATM, DW>, tm_w, tm_x, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, wq_gemm_tc_kernel<FMT, T, ATM, DW>, tm_w, tm_x, tm_y, p);
   if (e != cudaSuccess) {
     set_last_error("cudaLaunchKernelEx", e);
     return B200Q_ERR_CUDA;

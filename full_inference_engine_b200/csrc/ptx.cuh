@@ -120,6 +120,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// 3-D tiled store of a dense shared-memory tile (rows of box-width bytes); rows and columns
+// beyond the tensor's extents are clipped.  One thread issues; it then commits the bulk group
+// and waits until the tile has been READ (the shared memory may then be released or reused).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int32_t c0,
+                                             int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- TMEM
 // Whole-warp calls.  `ncols` is a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
