@@ -1055,8 +1055,8 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             continue;
           }
           alignas(8) T o[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
+          reinterpret_cast<uint32_t*>(o)[0] = pack_pair<T>(v[0] * sc[0] + bs[0], v[1] * sc[1] + bs[1]);
+          reinterpret_cast<uint32_t*>(o)[1] = pack_pair<T>(v[2] * sc[2] + bs[2], v[3] * sc[3] + bs[3]);
           T* dst = static_cast<T*>(p.y) + off;
           if (vec4 && reinterpret_cast<uintptr_t>(dst) % 8 == 0) {
             *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
@@ -1175,8 +1175,8 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                 continue;
               }
               alignas(8) T o[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) o[e] = from_float<T>(v[e] * sc[e] + bs[e]);
+              reinterpret_cast<uint32_t*>(o)[0] = pack_pair<T>(v[0] * sc[0] + bs[0], v[1] * sc[1] + bs[1]);
+              reinterpret_cast<uint32_t*>(o)[1] = pack_pair<T>(v[2] * sc[2] + bs[2], v[3] * sc[3] + bs[3]);
               const bool vec_store = vec4 && ((off * sizeof(T)) % 8 == 0);
               for (int d = 0; d < ndst; ++d) {
                 if (vec_store && reinterpret_cast<uintptr_t>(ydst[d]) % 8 == 0) {
@@ -1332,6 +1332,15 @@ static bool use_tmem_operand() {
   return v;
 }
 
+static int forced_dequant_warps() {
+  static const int v = [] {
+    const char* e = std::getenv("B200Q_TC_DW");
+    const int n = e ? std::atoi(e) : 0;
+    return (n == 8 || n == 16) ? n : 0;
+  }();
+  return v;
+}
+
 static TcPlan make_plan(int format, int M, int N, int K) {
   TcPlan pl{};
   pl.atm = use_tmem_operand();
@@ -1367,7 +1376,8 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   // stage there.  Each of their four column slices must be whole groups of 8 columns.
   // Large prefill problems (many waves) are MMA-bound and measured no better with them.
   pl.dw = 8;
-  if (pl.atm && tok > 64 && mt < 4) {
+  const int forced_dw = forced_dequant_warps();      // B200Q_TC_DW=8|16 overrides (experiments)
+  if (pl.atm && tok > 64 && (forced_dw ? forced_dw == 16 : mt < 4)) {
     tok = (tok + 31) / 32 * 32;
     pl.dw = 16;
   }
