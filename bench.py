@@ -46,8 +46,10 @@ SHAPES_8B = {"q": (4096, 4096), "kv": (4096, 2048), "o": (4096, 4096),
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; keyed like Case.key.  None = not captured.
 NCU_TRAFFIC_BYTES: dict[str, float] = {
-    "w4_asym:gate_up:M16": 26.91e6,      # profiles/wq_gemm_tc_int4_gate_up_M16.md
-    "w4_asym:gate_up:M4096": 133.6e6,    # profiles/wq_gemm_tc_int4_gate_up_M4096.md
+    "w4_asym:gate_up:M16": 26.97e6,      # profiles/wq_gemm_tc_int4_gate_up_M16.md
+    "w4_asym:gate_up:M256": 28.91e6,     # profiles/wq_gemm_tc_int4_M256.md
+    "w4_asym:down:M256": 33.11e6,        # profiles/wq_gemm_tc_int4_M256.md
+    "w4_asym:gate_up:M4096": 139.2e6,    # profiles/wq_gemm_tc_int4_gate_up_M4096.md
 }
 
 
