@@ -304,8 +304,8 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ void red_add_relaxed_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -523,7 +523,10 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         // whatever read its previous output has finished (it precedes us in the stream).
         grid_dependency_wait();
         const unsigned long long gen = p.g_sig[p.g_rank][kSigGeneration] + 1;
-        for (int d = 0; d < p.g_world; ++d) st_release_sys(p.g_sig[d] + kSigReady + p.g_rank, gen);
+        // Relaxed: the announcement publishes no data of this kernel, only that the kernels
+        // before it in the stream have finished (they have: griddepcontrol.wait returned).  A
+        // release store per peer would serialise one NVLink round trip per rank.
+        for (int d = 0; d < p.g_world; ++d) st_relaxed_sys(p.g_sig[d] + kSigReady + p.g_rank, gen);
       }
       bool ok = true;
       int sa = 0, sx = 0, xs = 0;                // operand stage, activation chunk slot, block in chunk
@@ -844,16 +847,13 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 #pragma unroll
     for (int d = 0; d < 8; ++d) ydst[d] = gather ? static_cast<T*>(p.g_y[d]) : static_cast<T*>(p.y);
     // Before the first store into another rank's buffer: that rank must have entered this call
-    // (its consumer of the previous call is done).  Bounded; one thread polls, the rest wait at
-    // the named barrier.
+    // (its consumer of the previous call is done).  Bounded; one lane per peer polls, the rest
+    // wait at the named barrier.
     auto gather_wait_ready = [&]() {
-      if (td == 0) {
+      if (td < p.g_world && td != p.g_rank) {       // one lane per peer, polled side by side
         unsigned long long* mine = p.g_sig[p.g_rank];
         const unsigned long long gen = mine[kSigGeneration] + 1;
-        for (int d = 0; d < p.g_world; ++d) {
-          if (d == p.g_rank) continue;
-          if (!poll_at_least(mine + kSigReady + d, gen)) mine[kSigStatus] = 2ull;
-        }
+        if (!poll_at_least(mine + kSigReady + td, gen)) mine[kSigStatus] = 2ull;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
     };
@@ -1585,12 +1585,14 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
     return B200Q_ERR_CUDA;
 
   // Output as {N_out, M, 1}: a finished tile [tok rows x tile_out columns] leaves shared memory
-  // through one TMA store.  Needs 16-byte aligned rows; the fused all-gather (peer pointers,
-  // one copy per rank) and split-K keep their own store paths.
+  // through one TMA store.  Needs 16-byte aligned rows of whole 16-byte units; the fused
+  // all-gather (peer pointers, one copy per rank) and split-K keep their own store paths.
   CUtensorMap tm_y{};
   const bool gathering = a.gather != nullptr && a.gather->world > 1;
   const int n_out = a.swiglu ? a.N / 2 : a.N;
-  const bool y_tma = ATM && !gathering && pl.splits == 1 && (a.ldy % 8 == 0) &&
+  // (The TMA engine clips the innermost dimension in 16-byte units: measured, a 500-column fp16
+  // output had columns 500..503 written.  So the row width must be whole 16-byte units too.)
+  const bool y_tma = ATM && !gathering && pl.splits == 1 && (a.ldy % 8 == 0) && (n_out % 8 == 0) &&
                      (reinterpret_cast<uintptr_t>(a.y) % 16 == 0) && tma_store_enabled();
   if (y_tma) {
     const CUtensorMapDataType ydt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
