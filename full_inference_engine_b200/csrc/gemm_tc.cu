@@ -1332,6 +1332,15 @@ static bool use_tmem_operand() {
   return v;
 }
 
+// B200Q_TC_WIDE_SMALL=0 keeps narrow token tiles on the two-blocks-per-SM shape always.
+static bool wide_small_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200Q_TC_WIDE_SMALL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+
 static int forced_dequant_warps() {
   static const int v = [] {
     const char* e = std::getenv("B200Q_TC_DW");
@@ -1377,7 +1386,16 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   // Large prefill problems (many waves) are MMA-bound and measured no better with them.
   pl.dw = 8;
   const int forced_dw = forced_dequant_warps();      // B200Q_TC_DW=8|16 overrides (experiments)
-  if (pl.atm && tok > 64 && (forced_dw ? forced_dw == 16 : mt < 4)) {
+  // "Wide" blocks own an SM (512 TMEM columns, up to 227 KB of shared memory).  Token tiles
+  // above 64 always are; a tile of 33..64 tokens also takes that shape when the problem has so
+  // few weight tiles that a 4-way K split inside a cluster fits in one wave: its partials
+  // (tok x 128 fp32 per block) then never leave the SMs.  Measured at M = 64: 4096x4096
+  // 16.3 -> 9.9 us, 12288->4096 23.9 -> 19.2 us; at 16 tokens the two-blocks-per-SM shape
+  // stays ahead (14.1 against 18.2 us), so narrower tiles keep it.
+  const int tiles0 = mt * ((N + kBlockN - 1) / kBlockN);
+  const bool wide = tok > 64 || (pl.atm && wide_small_enabled() && tok > 32 && 4 * tiles0 <= 148 &&
+                                 (K + kBlockK - 1) / kBlockK >= 32);
+  if (pl.atm && wide && (forced_dw ? forced_dw == 16 : mt < 4)) {
     tok = (tok + 31) / 32 * 32;
     pl.dw = 16;
   }
@@ -1393,7 +1411,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   const int xbytes = tok * 256;                    // activations of one K block (two atoms)
   const size_t a_stage_smem = pl.atm ? 0 : kStageBytesA;
   pl.xg = tok <= 16 ? 4 : (tok <= 32 ? 2 : 1);
-  pl.pg = tok <= 64 ? 2 : 1;
+  pl.pg = wide ? 1 : 2;
   auto total = [&](int np, int na, int nx) {
     return static_cast<size_t>(na) * a_stage_smem + static_cast<size_t>(nx) * pl.xg * xbytes +
            static_cast<size_t>(np) * pl.pg * pbytes + 1024 /*alignment*/ + 8 * kMaxRing * 6 + 64;
@@ -1409,7 +1427,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
     // Two resident blocks need <= 256 columns each: narrow tiles (decode, HBM-bound) take
     // that shape so one block's set-up and epilogue overlap the other's weight stream.
     pl.a_col0 = (tok + 63) / 64 * 64;
-    two_per_sm = tok <= 64 && total(2, 0, 2) <= half_sm;
+    two_per_sm = !wide && total(2, 0, 2) <= half_sm;
     if (two_per_sm) {
       pl.na = (256 - pl.a_col0) / 64;              // 3 for tok <= 64
       pl.nx = 3;
@@ -1463,7 +1481,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   if (max_splits > 16) max_splits = 16;
   if (max_splits < 1) max_splits = 1;
   int best = 1;
-  if (tok > 64) {
+  if (wide) {
     if (2 * tiles <= slots) {
       best = slots / tiles;
       const int cap = pl.kb_total / 8;         // a wide tile's split must be worth its reduction
