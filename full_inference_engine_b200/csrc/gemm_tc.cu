@@ -1332,13 +1332,14 @@ static bool use_tmem_operand() {
   return v;
 }
 
-// B200Q_TC_WIDE_SMALL=0 keeps narrow token tiles on the two-blocks-per-SM shape always.
-static bool wide_small_enabled() {
-  static const bool on = [] {
+// Most weight tiles a problem may have for its 33..64-token tiles to take the wide block shape.
+// B200Q_TC_WIDE_SMALL=<n> overrides it (0: never).
+static int wide_small_max_tiles() {
+  static const int n = [] {
     const char* v = std::getenv("B200Q_TC_WIDE_SMALL");
-    return !(v != nullptr && v[0] == '0');
+    return v != nullptr ? std::atoi(v) : 74;
   }();
-  return on;
+  return n;
 }
 
 static int forced_dequant_warps() {
@@ -1388,12 +1389,13 @@ static TcPlan make_plan(int format, int M, int N, int K) {
   const int forced_dw = forced_dequant_warps();      // B200Q_TC_DW=8|16 overrides (experiments)
   // "Wide" blocks own an SM (512 TMEM columns, up to 227 KB of shared memory).  Token tiles
   // above 64 always are; a tile of 33..64 tokens also takes that shape when the problem has so
-  // few weight tiles that a 4-way K split inside a cluster fits in one wave: its partials
-  // (tok x 128 fp32 per block) then never leave the SMs.  Measured at M = 64: 4096x4096
-  // 16.3 -> 9.9 us, 12288->4096 23.9 -> 19.2 us; at 16 tokens the two-blocks-per-SM shape
-  // stays ahead (14.1 against 18.2 us), so narrower tiles keep it.
+  // few weight tiles (at most half a wave) that a K split inside a cluster fits in one wave:
+  // its partials (tok x 128 fp32 per block) then never leave the SMs.  Measured at M = 64:
+  // 4096x4096 16.3 -> 9.9 us, 4096->8192 16.3 -> 13.5 us, 12288->4096 23.9 -> 19.2 us; a full
+  // wave of unsplit wide tiles (4096->12288) ties with the narrow shape, and at 16 tokens two
+  // blocks per SM stay ahead (14.1 against 18.2 us), so those keep the narrow shape.
   const int tiles0 = mt * ((N + kBlockN - 1) / kBlockN);
-  const bool wide = tok > 64 || (pl.atm && wide_small_enabled() && tok > 32 && 4 * tiles0 <= 148 &&
+  const bool wide = tok > 64 || (pl.atm && tok > 32 && tiles0 <= wide_small_max_tiles() &&
                                  (K + kBlockK - 1) / kBlockK >= 32);
   if (pl.atm && wide && (forced_dw ? forced_dw == 16 : mt < 4)) {
     tok = (tok + 31) / 32 * 32;
