@@ -152,7 +152,7 @@ def test_other_group_sizes_take_the_cuda_core_kernel(g):
 
 @pytest.mark.parametrize("shape", [(4096, 12288), (12288, 4096)])
 def test_config2_int4_m_sweep_at_qwen3_8b_mlp_shapes(shape):
-    """BASELINE config 2: INT4 g128, fp16 activations, M in {1,4,16,64,256}, both layouts."""
+    """benchmark configuration 2: INT4 g128, fp16 activations, M in {1,4,16,64,256}, both layouts."""
     k, n = shape
     torch.manual_seed(0)
     weight = (torch.randn(n, k) * 0.02).cuda()
@@ -174,7 +174,7 @@ def test_config2_int4_m_sweep_at_qwen3_8b_mlp_shapes(shape):
 
 @pytest.mark.parametrize("shape", [(4096, 4096), (4096, 2048), (4096, 12288), (12288, 4096)])
 def test_config4_w8_bf16_at_qwen3_8b_shapes(shape):
-    """BASELINE config 4 (one GPU's view): W8 per-channel, bf16 activations."""
+    """benchmark configuration 4 (one GPU's view): W8 per-channel, bf16 activations."""
     k, n = shape
     torch.manual_seed(0)
     q, s = w8a16_linear.quantize_weight_per_channel((torch.randn(n, k) * 0.02).cuda())
@@ -188,7 +188,7 @@ def test_config4_w8_bf16_at_qwen3_8b_shapes(shape):
 
 @pytest.mark.parametrize("shape", [(4096, 12288), (12288, 4096)])
 def test_config5_prefill_with_outlier_rows(shape):
-    """BASELINE config 5: M=4096 bf16, 1% of rows x20.  The oracle checks a sample of rows
+    """benchmark configuration 5: M=4096 bf16, 1% of rows x20.  The oracle checks a sample of rows
     (all outlier rows among them); the whole output is checked against torch's fp32 matmul
     over the oracle-identical dequantised weights."""
     k, n = shape

@@ -2,7 +2,7 @@
 packed weights run through torch (``reference_mode``), CUDA-graph capture and replay of a
 mixed step, the streaming loader on the GPU.  Follows the reference's
 tests/quantization/test_w4a16_cuda.py with random-init models (no checkpoint is available
-offline) and BASELINE config 3 for the graph test."""
+offline) and benchmark configuration 3 for the graph test."""
 
 from __future__ import annotations
 
@@ -128,7 +128,7 @@ class _Block(nn.Module):
 
 
 def _projection_stack(layers=28, hidden=1024, heads=16, kv=8, head_dim=128, inter=3072):
-    """BASELINE config 3: the seven Qwen3-0.6B projections of every layer, random-init."""
+    """benchmark configuration 3: the seven Qwen3-0.6B projections of every layer, random-init."""
     torch.manual_seed(0)
     stack = nn.Sequential(*[_Block(hidden, heads, kv, head_dim, inter) for _ in range(layers)])
     for p in stack.parameters():
