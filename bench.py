@@ -96,6 +96,9 @@ def build_cases(workload: str, layout: str) -> list[Case]:
                 for name in ("q", "kv", "o", "gate_up", "down") for m in (1, 16, 64, 512)]
     if workload == "c1":
         return [Case("gate_0p6b", "w8", 8, 1024, 3072, torch.float16)]
+    if workload == "head":
+        # the reference's largest single matrix: the Qwen3-8B output head (4096 -> 151936)
+        return [Case("lm_head", w4, m, 4096, 151936, torch.float16) for m in (1, 16, 256)]
     if workload == "mlp":
         # beyond the reference: gate_proj + up_proj + silu(gate) * up of a Qwen3-8B feed-forward
         # as ONE launch over interleaved quantized rows (2 x 12288 rows of K = 4096)
@@ -361,6 +364,8 @@ def config_dict(args, cases, rotation):
                            "gate/up and down",
                      "c4": "config 4: W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, M in {1,16,64,512}",
                      "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16",
+                     "head": "the Qwen3-8B output head, INT4 g128 4096 -> 151936 (the reference's largest "
+                             "matrix, benchmarks/kernels/w4a16_bench.py), M in {1,16,256}, fp16",
                      "mlp": "beyond the reference: INT4 g128 gate_proj + up_proj + silu(gate) * up of a "
                             "Qwen3-8B feed-forward (K=4096, 2 x 12288 interleaved rows) in one launch, "
                             "M in {1,16,64,256,1024}, fp16; per_case carries the two-projections-plus-"
@@ -416,7 +421,7 @@ def run_b200(args, cases):
             print(f"# rank {rank}: {msg}", file=sys.stderr, flush=True)
 
     pk = peaks()
-    copies = {"c1": 48, "c2": 10, "c3": 1, "c4": 4, "c5": 6, "mlp": 6}[args.workload]
+    copies = {"c1": 48, "c2": 10, "c3": 1, "c4": 4, "c5": 6, "mlp": 6, "head": 2}[args.workload]
     weight_sets = make_weight_sets(cases, copies, device, rank, world)
     acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
     # per-rank view of each case
@@ -768,7 +773,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "mlp"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "mlp", "head"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
