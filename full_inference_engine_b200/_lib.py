@@ -22,6 +22,7 @@ W4_REF_SPLIT_HALF_SYM, W4_ASYM_ZP_INT32 = 0, 1
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
 FLAG_STATIC_WEIGHTS = 0x100
 FLAG_SWIGLU_PAIRS = 0x200
+FLAG_ARGMAX = 0x400
 W8_SCALE_F16, W8_SCALE_F32 = 0, 1
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_WAIT = range(7)
 

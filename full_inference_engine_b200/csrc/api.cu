@@ -39,6 +39,12 @@ constexpr int kSimtMaxRowsW8 = 1;
 static int run_forward(ForwardArgs& a, int kernel_and_flags) {
   a.static_weights = (kernel_and_flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
   const int kernel = kernel_and_flags & 0xFF;
+  if (a.argmax) {
+    // the row-wise argmax epilogue exists in the tensor-core kernel (A operand in tensor
+    // memory) only, and not together with the gated pairs
+    if (a.swiglu || (kernel != B200Q_KERNEL_AUTO && kernel != B200Q_KERNEL_TC)) return B200Q_ERR_UNSUPPORTED;
+    return launch_forward_tc(a);
+  }
   if (a.swiglu) {
     // the gated-pair epilogue exists in the tensor-core kernel only
     if (kernel != B200Q_KERNEL_AUTO && kernel != B200Q_KERNEL_TC) return B200Q_ERR_UNSUPPORTED;
@@ -142,10 +148,13 @@ int b200q_w8a16_forward(const void* x, int64_t ldx, int act_dtype, const int8_t*
   if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
   const bool swiglu = (kernel & B200Q_FLAG_SWIGLU_PAIRS) != 0;
   if (swiglu && (N & 1)) return B200Q_ERR_INVALID;
-  if (ldx < K || ldw < K || ldy < (swiglu ? N / 2 : N)) return B200Q_ERR_INVALID;
+  const bool argmax = (kernel & B200Q_FLAG_ARGMAX) != 0;
+  if (ldx < K || ldw < K || (!argmax && ldy < (swiglu ? N / 2 : N))) return B200Q_ERR_INVALID;
+  if (argmax && reinterpret_cast<uintptr_t>(y) % 8) return B200Q_ERR_ALIGNMENT;
   if (K % 16) return B200Q_ERR_UNSUPPORTED;
   ForwardArgs a{};
   a.swiglu = swiglu;
+  a.argmax = argmax;
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
   a.w = qweight; a.ldw = ldw; a.format = FMT_W8;
   a.scales = scales; a.scale_dtype = scale_dtype; a.zeros = nullptr; a.group = 0;
@@ -172,9 +181,12 @@ int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype, const void* p
   if (group % 32) return B200Q_ERR_UNSUPPORTED;
   const bool swiglu = (kernel & B200Q_FLAG_SWIGLU_PAIRS) != 0;
   if (swiglu && (N & 1)) return B200Q_ERR_INVALID;
-  if (ldx < K || ldw < K / 2 || ldy < (swiglu ? N / 2 : N)) return B200Q_ERR_INVALID;
+  const bool argmax = (kernel & B200Q_FLAG_ARGMAX) != 0;
+  if (ldx < K || ldw < K / 2 || (!argmax && ldy < (swiglu ? N / 2 : N))) return B200Q_ERR_INVALID;
+  if (argmax && reinterpret_cast<uintptr_t>(y) % 8) return B200Q_ERR_ALIGNMENT;
   ForwardArgs a{};
   a.swiglu = swiglu;
+  a.argmax = argmax;
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
   a.w = packed; a.ldw = ldw;
   a.format = layout == B200Q_W4_ASYM_ZP_INT32 ? FMT_W4_ASYM : FMT_W4_REF;
@@ -217,7 +229,7 @@ int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   }
   if (group <= 0 || K % group) return B200Q_ERR_INVALID;
   if (ldx < K || ldw < K / 2) return B200Q_ERR_INVALID;
-  if (flags & B200Q_FLAG_SWIGLU_PAIRS) return B200Q_ERR_INVALID;
+  if (flags & (B200Q_FLAG_SWIGLU_PAIRS | B200Q_FLAG_ARGMAX)) return B200Q_ERR_INVALID;
   if (int st = check_gather(gather, ldy, N_local)) return st;
   ForwardArgs a{};
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
@@ -242,7 +254,7 @@ int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
   if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
   if (ldx < K || ldw < K) return B200Q_ERR_INVALID;
-  if (flags & B200Q_FLAG_SWIGLU_PAIRS) return B200Q_ERR_INVALID;
+  if (flags & (B200Q_FLAG_SWIGLU_PAIRS | B200Q_FLAG_ARGMAX)) return B200Q_ERR_INVALID;
   if (int st = check_gather(gather, ldy, N_local)) return st;
   ForwardArgs a{};
   a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;

@@ -69,6 +69,8 @@ struct TcParams {
   int static_weights;  // weights/scales/bias may be read ahead of the stream order
   int swiglu;          // rows are (gate, up) pairs: y[m, c] = silu(row 2c) * row 2c+1; N/2 output columns
   int y_tma;           // finished tiles leave shared memory through one TMA store (tm_y is valid)
+  int argmax;          // y is int64 channel[M]: per row the channel of the largest output
+  unsigned long long* row_keys;  // [M] in the workspace, zero between launches (argmax only)
   // fused all-gather (g_world > 1): every output tile is stored into the [M, ldy] buffer of
   // every rank at column offset g_col0, through peer-mapped pointers
   int g_world, g_rank, g_col0;
@@ -874,7 +876,69 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                                   : __half2float(reinterpret_cast<const __half*>(p.scales)[n]);
       if (p.bias != nullptr) ch_bias = static_cast<float>(static_cast<const T*>(p.bias)[n]);
     }
-    if (p.splits == 1) {
+    if (p.argmax) {
+      // Row-wise argmax instead of the outputs (greedy decoding over an output head): every
+      // value is rounded to the activation dtype exactly as the plain path would store it,
+      // mapped to an order-preserving 16-bit code, and reduced warp -> block (shared-memory
+      // atomics) -> grid (one 64-bit atomicMax per row and tile on keys in the workspace).
+      // Key = code << 32 | (0xFFFFFFFF - channel): the largest value wins, ties go to the
+      // smallest channel.
+      volatile uint32_t* best = reinterpret_cast<volatile uint32_t*>(generic_base + (x_ring - smem_base));
+      for (int t = td; t < p.tok; t += kDequantThreads) best[t] = 0u;
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      if (acc_ok && nkb > 0) {
+        for (int c = 0; c < half_cols; c += 8) {
+          uint32_t r[8];
+          tmem_ld_x8(tmem_row + (c_begin + c), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const uint32_t two = pack_pair<T>(__uint_as_float(r[j]) * ch_scale + ch_bias,
+                                              __uint_as_float(r[j + 1]) * ch_scale + ch_bias);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t bits = h ? (two >> 16) : (two & 0xFFFFu);
+              const uint32_t code = (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
+              const uint32_t key = (n < p.N) ? ((code << 16) | static_cast<uint32_t>(kBlockN - 1 - ch)) : 0u;
+              const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+              if (lane == 0 && top != 0u)
+                atomicMax(const_cast<uint32_t*>(best) + (c_begin + c + j + h), top);
+            }
+          }
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      const int rows = min(p.tok, p.M - m_base);
+      for (int t = td; t < rows; t += kDequantThreads) {
+        const uint32_t top = best[t];
+        if (top != 0u) {
+          const uint32_t channel = static_cast<uint32_t>(n_tile * kBlockN + (kBlockN - 1 - static_cast<int>(top & 0xFFFFu)));
+          const unsigned long long key64 =
+              (static_cast<unsigned long long>(top >> 16) << 32) | (0xFFFFFFFFull - channel);
+          atomicMax(p.row_keys + (m_base + t), key64);
+        }
+      }
+      if (td == 0) B200Q_STAMP(57);
+      // The last block of the grid to get here turns the keys into channel indices and puts
+      // keys and counter back to zero for the next launch (same protocol as split-K).
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      if (td == 0) {
+        const unsigned prev = atomicAdd(p.counters, 1u);
+        *last_p = (prev == gridDim.x * gridDim.y - 1u) ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kDequantThreads) : "memory");
+      if (*last_p) {
+        __threadfence();
+        long long* out = static_cast<long long*>(p.y);
+        for (int t = td; t < p.M; t += kDequantThreads) {
+          const unsigned long long key = __ldcg(p.row_keys + t);
+          out[t] = static_cast<long long>(0xFFFFFFFFull - (key & 0xFFFFFFFFull)) * (key != 0ull);
+          p.row_keys[t] = 0ull;
+        }
+        if (td == 0) *p.counters = 0u;
+      }
+    } else if (p.splits == 1) {
       if (gather) gather_wait_ready();
       // accumulators -> output dtype -> shared memory as dense rows [token][tile_out channels]
       // (the operand rings are idle by now), then either ONE TMA store of the whole tile
@@ -1351,7 +1415,7 @@ static int forced_dequant_warps() {
   return v;
 }
 
-static TcPlan make_plan(int format, int M, int N, int K) {
+static TcPlan make_plan(int format, int M, int N, int K, bool no_split = false) {
   TcPlan pl{};
   pl.atm = use_tmem_operand();
   // Token tile: as few tiles as cover M, except that a problem of at most two waves (148
@@ -1503,7 +1567,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
       if (eff >= 0.9) break;
     }
   }
-  if (tiles >= slots || tiles > kMaxSplitTiles || best < 1) best = 1;
+  if (tiles >= slots || tiles > kMaxSplitTiles || best < 1 || no_split) best = 1;
   pl.kb_per_split = (pl.kb_total + best - 1) / best;
   pl.splits = (pl.kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
   return pl;
@@ -1512,7 +1576,7 @@ static TcPlan make_plan(int format, int M, int N, int K) {
 size_t tc_workspace_bytes(int format, int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   TcPlan pl = make_plan(format, M, N, K);
-  size_t bytes = kWsHeaderBytes;
+  size_t bytes = kWsHeaderBytes + 8 * static_cast<size_t>(M);    // header + the argmax keys
   if (pl.splits > 1) bytes += sizeof(float) * static_cast<size_t>(pl.splits) * M * N;
   return bytes;
 }
@@ -1612,7 +1676,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   const int n_out = a.swiglu ? a.N / 2 : a.N;
   // (The TMA engine clips the innermost dimension in 16-byte units: measured, a 500-column fp16
   // output had columns 500..503 written.  So the row width must be whole 16-byte units too.)
-  const bool y_tma = ATM && !gathering && pl.splits == 1 && (a.ldy % 8 == 0) && (n_out % 8 == 0) &&
+  const bool y_tma = ATM && !gathering && !a.argmax && pl.splits == 1 && (a.ldy % 8 == 0) && (n_out % 8 == 0) &&
                      (reinterpret_cast<uintptr_t>(a.y) % 16 == 0) && tma_store_enabled();
   if (y_tma) {
     const CUtensorMapDataType ydt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -1650,6 +1714,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.xg = pl.xg;
   p.static_weights = a.static_weights ? 1 : 0;
   p.swiglu = a.swiglu ? 1 : 0;
+  p.argmax = a.argmax ? 1 : 0;
   p.g_world = 0;
   if (a.gather != nullptr && a.gather->world > 1) {
     p.g_world = a.gather->world;
@@ -1664,6 +1729,7 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   p.status = reinterpret_cast<unsigned*>(ws);
   p.counters = reinterpret_cast<unsigned*>(ws + 256);
   p.partial = reinterpret_cast<float*>(ws + kWsHeaderBytes);
+  p.row_keys = reinterpret_cast<unsigned long long*>(ws + kWsHeaderBytes);   // argmax never splits K
 
   // Programmatic dependent launch: this grid may begin its set-up (and, with static
   // weights, its weight stream) while the previous kernel of the stream drains; the
@@ -1769,7 +1835,7 @@ int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaS
 int launch_forward_tc(const ForwardArgs& a) {
   if (a.M <= 0 || a.N <= 0) return B200Q_OK;
   if (!tc_supported(a)) return B200Q_ERR_UNSUPPORTED;
-  const TcPlan pl = make_plan(a.format, a.M, a.N, a.K);
+  const TcPlan pl = make_plan(a.format, a.M, a.N, a.K, a.argmax);
   const size_t need = tc_workspace_bytes(a.format, a.M, a.N, a.K);
   if (a.workspace == nullptr || a.workspace_bytes < need) return B200Q_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(a.workspace) % 256) return B200Q_ERR_ALIGNMENT;

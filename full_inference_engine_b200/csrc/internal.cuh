@@ -33,6 +33,7 @@ struct ForwardArgs {
   size_t workspace_bytes;
   bool static_weights;  // weights/scales/zeros/bias were written long before this call
   bool swiglu;          // rows are interleaved (gate, up) pairs; y has N/2 columns of silu(gate) * up
+  bool argmax;          // y is u64 keys[M], zeroed by the caller: row-wise maximum and its channel
   const b200q_gather* gather;  // fused all-gather destinations, or null
   cudaStream_t stream;
 };

@@ -19,7 +19,7 @@ _KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERN
 
 
 def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, static_weights=False,
-             swiglu_pairs=False):
+             swiglu_pairs=False, argmax=False):
     _lib.require_cuda(inputs, "inputs")
     m, k = inputs.shape
     n = packed.shape[0]
@@ -40,11 +40,14 @@ def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, sta
     if bias is not None:
         b = bias if (bias.dtype is inputs.dtype and bias.is_contiguous()) \
             else bias.to(inputs.dtype).contiguous()
-    out = torch.empty((m, n // 2 if swiglu_pairs else n), dtype=inputs.dtype, device=inputs.device)
+    if argmax:      # one channel index per row instead of the [M, N] outputs
+        out = torch.empty((m,), dtype=torch.int64, device=inputs.device)
+    else:
+        out = torch.empty((m, n // 2 if swiglu_pairs else n), dtype=inputs.dtype, device=inputs.device)
     if m == 0 or n == 0:
         return out
     flags = (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0) \
-        | (_lib.FLAG_SWIGLU_PAIRS if swiglu_pairs else 0)
+        | (_lib.FLAG_SWIGLU_PAIRS if swiglu_pairs else 0) | (_lib.FLAG_ARGMAX if argmax else 0)
     need = _lib.workspace_bytes(4, m, n, k)
     ws = _lib.workspace_for(inputs.device, need)
     layout = _lib.W4_REF_SPLIT_HALF_SYM if zeros is None else _lib.W4_ASYM_ZP_INT32
@@ -64,7 +67,8 @@ def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tenso
                  bias: torch.Tensor | None = None, *, group_size: int = GROUP_SIZE,
                  block_m: int = 16, block_n: int = 64, num_warps: int = 4,
                  kernel: str = "auto", zeros: torch.Tensor | None = None,
-                 static_weights: bool = False, swiglu_pairs: bool = False) -> torch.Tensor:
+                 static_weights: bool = False, swiglu_pairs: bool = False,
+                 _argmax: bool = False) -> torch.Tensor:
     """``inputs [M, K]`` x dequantised ``packed/scales`` -> ``[M, N]`` in ``inputs.dtype``.
 
     Reference: ``w4a16_linear`` (engine/kernels/w4a16_linear.py:77-117).  With ``zeros``
@@ -96,7 +100,7 @@ def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tenso
     if swiglu_pairs and n % 2:
         raise ValueError("gate/up pairs need an even number of weight rows")
     return _forward(inputs, packed, scales, zeros, bias, group_size, _KERNELS[kernel], "w4a16_linear",
-                    static_weights, swiglu_pairs)
+                    static_weights, swiglu_pairs, _argmax)
 
 
 def w4a16_gemv(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,

@@ -45,7 +45,8 @@ def quantize_weight_per_channel_fp32_scales(weight: torch.Tensor) -> tuple[torch
 
 def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
                  bias: torch.Tensor | None = None, *, kernel: str = "auto",
-                 static_weights: bool = False, swiglu_pairs: bool = False) -> torch.Tensor:
+                 static_weights: bool = False, swiglu_pairs: bool = False,
+                 _argmax: bool = False) -> torch.Tensor:
     """W8A16 linear for 2-D activations (engine/kernels/w8a16_linear.py:50-69).
 
     The integer weights enter the multiply unscaled (they are exact in fp16 and bf16);
@@ -77,11 +78,14 @@ def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tens
     if bias is not None:
         b = bias if (bias.dtype is inputs.dtype and bias.is_contiguous()) \
             else bias.to(inputs.dtype).contiguous()
-    out = torch.empty((m, n // 2 if swiglu_pairs else n), dtype=inputs.dtype, device=inputs.device)
+    if _argmax:     # one channel index per row instead of the [M, N] outputs
+        out = torch.empty((m,), dtype=torch.int64, device=inputs.device)
+    else:
+        out = torch.empty((m, n // 2 if swiglu_pairs else n), dtype=inputs.dtype, device=inputs.device)
     if m == 0 or n == 0:
         return out
     flags = (_lib.FLAG_STATIC_WEIGHTS if static_weights else 0) \
-        | (_lib.FLAG_SWIGLU_PAIRS if swiglu_pairs else 0)
+        | (_lib.FLAG_SWIGLU_PAIRS if swiglu_pairs else 0) | (_lib.FLAG_ARGMAX if _argmax else 0)
     ws = _lib.workspace_for(inputs.device, _lib.workspace_bytes(8, m, n, k))
     with torch.cuda.device(inputs.device):
         _lib.check(_lib.library().b200q_w8a16_forward(

@@ -131,6 +131,19 @@ class W4A16Linear(nn.Module):
                                   group_size=self.group_size, static_weights=True).to(x.dtype)
         return out.reshape(*x.shape[:-1], self.out_features)
 
+    def argmax(self, x: torch.Tensor) -> torch.Tensor:
+        """``self(x).argmax(-1)`` (greedy decoding over an output head) without writing the
+        ``[..., out_features]`` outputs: the kernel's epilogue keeps each row's maximum."""
+        if self.reference or x.device.type != "cuda":
+            return self.forward(x).argmax(dim=-1)
+        from ..kernels.argmax import w4a16_linear_argmax
+
+        rows = x.reshape(-1, self.in_features)
+        compute = rows if rows.dtype in (torch.float16, torch.bfloat16) else rows.to(torch.float16)
+        channels = w4a16_linear_argmax(compute, self.packed, self.scales, self.bias,
+                                       group_size=self.group_size, static_weights=True)
+        return channels.reshape(x.shape[:-1])
+
     def _reference_forward(self, rows: torch.Tensor) -> torch.Tensor:
         """Dequantise (whole, or in N slabs above ``dense_slab_bytes``) and ``F.linear``."""
         bias = None if self.bias is None else self.bias.to(rows.dtype)

@@ -82,6 +82,16 @@ typedef enum b200q_kernel {
  * (B200Q_ERR_UNSUPPORTED with B200Q_KERNEL_SIMT or an unsupported geometry); not accepted
  * by the *_forward_gather entry points.                                                   */
 #define B200Q_FLAG_SWIGLU_PAIRS 0x200
+/* ARGMAX: instead of the [M, N] outputs the call writes, for every row, the channel of its
+ * largest output (greedy decoding over a quantized output head; the reference runs lm_head
+ * and then torch.argmax over the [M, vocab] logits).  `y` points at M int64 values; `ldy` is
+ * ignored.  Every output is rounded to the activation dtype exactly as the plain call would
+ * store it before it is compared, and among equal values the smallest channel wins, so the
+ * result equals argmax over the plain call's own output.  One launch: per-row keys live in the
+ * workspace (which must be zero before the first call, as for split-K) and the last block of
+ * the grid converts them and puts them back to zero.  Tensor-core kernel only; not with
+ * SWIGLU_PAIRS, not in the *_forward_gather entry points.                                   */
+#define B200Q_FLAG_ARGMAX 0x400
 
 /* W8 quantizer flavours */
 typedef enum b200q_w8_mode {

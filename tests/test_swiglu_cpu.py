@@ -139,3 +139,9 @@ def test_install_and_uninstall():
     assert uninstall_fused_swiglu(model) == 2
     assert isinstance(model[0].gate_proj, W4A16Linear) and not hasattr(model[0], "fused_gate_up_swiglu")
     assert torch.equal(model(x), before)
+
+
+def test_argmax_flag_value_matches_the_header():
+    header = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "b200q.h")
+    value = int(re.search(r"#define\s+B200Q_FLAG_ARGMAX\s+(0x[0-9a-fA-F]+)", open(header).read()).group(1), 16)
+    assert value == _lib.FLAG_ARGMAX and value & (_lib.FLAG_SWIGLU_PAIRS | _lib.FLAG_STATIC_WEIGHTS | 0xFF) == 0
