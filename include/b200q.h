@@ -153,7 +153,9 @@ int b200q_w4_dequant(const void* packed, const void* scales, const void* zeros,
  * Bytes of workspace a forward call of this geometry may use (0 = none).
  * `format`: 8 for W8A16, 4 for either INT4 layout.  The workspace must be
  * zero-filled once when it is allocated; every call leaves it zeroed again
- * where that matters, so graph replays need no memset.
+ * where that matters, so graph replays need no memset.  Calls that may overlap
+ * on the GPU (different streams) need a workspace each: split-K counters,
+ * partials and argmax keys of two running kernels must not share memory.
  */
 size_t b200q_workspace_bytes(int format, int M, int N, int K);
 
