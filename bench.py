@@ -669,6 +669,36 @@ def run_b200(args, cases):
         entry.update(roofline_entry(case, sec, pk))
         entry["frac_of_nominal"] = round(
             max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
+        if args.workload == "head" and case.fmt != "w8":
+            # greedy decoding over the head: projection + torch.argmax against the fused epilogue
+            from full_inference_engine_b200.kernels import argmax as fused_argmax
+
+            def pick(w, fused):
+                z = w[2] if len(w) > 2 else None
+                if fused:
+                    return fused_argmax.w4a16_linear_argmax(acts[i], w[0], w[1], zeros=z, static_weights=True)
+                return forward(case, acts[i], w).argmax(dim=-1)
+
+            for label, fused in (("argmax_after_us", False), ("argmax_fused_us", True)):
+                assert torch.equal(pick(sets[0], True), pick(sets[0], False))
+                torch.cuda.synchronize()
+                g3 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g3):
+                    for w in sets:
+                        pick(w, fused)
+                for _ in range(3):
+                    g3.replay()
+                torch.cuda.synchronize()
+                t3 = []
+                for _ in range(7):
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    g3.replay()
+                    e.record()
+                    torch.cuda.synchronize()
+                    t3.append(s.elapsed_time(e) / reps)
+                entry[label] = round(statistics.median(t3) * 1e3, 2)
+                del g3
         if case.swiglu:
             # the same work as two projections + an elementwise kernel, same protocol
             halves = [tuple(tuple(t[part::2].contiguous() for t in w) for part in (0, 1)) for w in sets]
