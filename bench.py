@@ -1,23 +1,34 @@
 """Benchmark of the weight-only quantized linear forward on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload c2|c5|c4|c1] [--layout asym|ref]
+                    [--workload all|c1|c2|c3|c4|c5|mlp|head] [--layout asym|ref]
 
 A *step* is one pass of the hot path over every case of the workload (one forward per
-(shape, M) pair) on synthetic seeded tensors.  The default workload ``c2`` is the INT4
-group-128 M-sweep at the Qwen3-8B MLP shapes; ``c5`` the M=4096 prefill GEMM; ``c4`` the
-W8A16 bf16 sweep; ``c1`` the single W8A16 case the reference runs on CPU.
+(format, shape, M) case) on synthetic seeded tensors.  The default workload ``all`` is the
+union of the benchmark configurations 1, 2, 4 and 5: the single W8A16 case the reference runs
+on CPU, the INT4 group-128 M-sweep at the Qwen3-8B MLP shapes (fp16), the W8A16 bf16 sweep
+over the Qwen3-8B attention and MLP shapes, and the M=4096 INT4 prefill GEMM with outlier rows
+(bf16) — 33 cases, M from 1 to 4096.  ``c1`` … ``c5`` select one configuration (``c3`` is the
+graph-captured mixed step of 196 Qwen3-0.6B projections).
 
 ``value`` is algorithmic GB/s over the whole step with inputs resident in HBM (CUDA-graph
-replay, two weight sets alternated so every weight byte comes from HBM, not L2).  ``e2e`` is
-the same metric through the Python module API with activations in pinned host memory:
-host->device copy, forward, device->host copy of the result, every step.  ``per_case``
-lists every (shape, M) with its own latency, GB/s, TFLOP/s and fraction of roofline, and
-``roofline`` repeats the entry of the kernel that takes the largest share of the step.
-``cpu_baseline`` times the reference's CPU path (dequantise to the activation dtype +
-``F.linear``) on the host cores in the same run.
+replay; every launch reads its own weight buffer and step variants alternate, so that every
+weight byte comes from HBM, not L2).  ``e2e`` is the same metric through the Python module API
+with activations in pinned host memory: host->device copy, forward, device->host copy of the
+result, every step.  ``per_case`` lists every case with its own latency, GB/s, TFLOP/s, the
+kernel instantiation that served it and its fraction of the roofline that bounds it;
+``roofline`` aggregates the cases of the instantiation with the largest share of the step;
+``roofline_by_regime`` aggregates the HBM-bound decode cases (M <= 16) and the tensor-bound
+prefill cases (M >= 2048).  ``cpu_baseline`` times the reference's CPU path (dequantise to the
+activation dtype + ``F.linear``) on the host cores in the same run, whole and split into its
+dequantise and matmul halves.
 
-With ``--impl reference`` only that CPU path runs (rank 0 only under torchrun).
+At ``--gpus N`` (N > 1, under torchrun) every matrix is sharded along its output channels; the
+line's ``phases`` give the sharded GEMMs alone, GEMM + all-gather fused into the kernel
+epilogue, and GEMM + NCCL all-gather, per step and per case, and ``gather_parity`` compares
+every case's gathered output with this rank's own single-GPU forward of the whole matrix.
+
+With ``--impl reference`` only the CPU path runs (rank 0 only under torchrun).
 """
 
 from __future__ import annotations
@@ -44,72 +55,104 @@ SHAPES_8B = {"q": (4096, 4096), "kv": (4096, 2048), "o": (4096, 4096),
              "gate_up": (4096, 12288), "down": (12288, 4096)}
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; keyed like Case.key.  None = not captured.
+# summarised under profiles/; keyed like Case.key.  Absent = not captured.
 NCU_TRAFFIC_BYTES: dict[str, float] = {
-    "w4_asym:gate_up:M16": 26.97e6,      # profiles/wq_gemm_tc_int4_gate_up_M16.md
     "w4_asym:gate_up:M256": 28.91e6,     # profiles/wq_gemm_tc_int4_M256.md
     "w4_asym:down:M256": 33.11e6,        # profiles/wq_gemm_tc_int4_M256.md
     "w4_asym:gate_up:M4096": 139.2e6,    # profiles/wq_gemm_tc_int4_gate_up_M4096.md
 }
 
+WORKLOAD_TEXT = {
+    "all": "configs 1,2,4,5: W8A16 M=8 1024->3072 fp16; INT4 g128 M in {1,4,16,64,256} at Qwen3-8B "
+           "gate/up (4096->12288) and down (12288->4096), fp16; W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, "
+           "M in {1,16,64,512}; INT4 g128 prefill M=4096 bf16 with 1% outlier rows, gate/up and down",
+    "c2": "config 2: INT4 g128 M-sweep {1,4,16,64,256} at Qwen3-8B gate/up (4096->12288) and down "
+          "(12288->4096), fp16 activations",
+    "c5": "config 5: INT4 g128 prefill M=4096 bf16 with 1% outlier rows, gate/up and down",
+    "c4": "config 4: W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, M in {1,16,64,512}",
+    "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16",
+    "head": "the Qwen3-8B output head, INT4 g128 4096 -> 151936 (the reference's largest matrix, "
+            "benchmarks/kernels/w4a16_bench.py), M in {1,16,256}, fp16",
+    "mlp": "beyond the reference: INT4 g128 gate_proj + up_proj + silu(gate) * up of a Qwen3-8B "
+           "feed-forward (K=4096, 2 x 12288 interleaved rows) in one launch, M in {1,16,64,256,1024}, "
+           "fp16; per_case carries the two-projections-plus-elementwise time beside it",
+    "c3": "config 3: 28 x 7 random-init Qwen3-0.6B W8A16 projections, one mixed step of M=144 rows "
+          "(16 decode + 128 prefill), fp16, one CUDA graph",
+}
+
 
 class Case:
-    def __init__(self, name, fmt, m, k, n, dtype, outliers=False, swiglu=False):
+    def __init__(self, name, fmt, m, k, n, dtype, outliers=False, swiglu=False, cfg=""):
         self.name, self.fmt, self.m, self.k, self.n = name, fmt, m, k, n
         self.dtype, self.outliers = dtype, outliers
         # n rows are interleaved (gate, up) pairs and the output is silu(gate) * up, n / 2 wide
         self.swiglu = swiglu
+        self.cfg = cfg
 
     @property
     def key(self):
         return f"{self.fmt}:{self.name}:M{self.m}"
 
     @property
+    def wkey(self):
+        return (self.fmt, self.name)
+
+    @property
     def flops(self):
         return 2.0 * self.m * self.n * self.k
 
-    def weight_bytes(self):
+    def weight_bytes(self, fmt=None):
+        fmt = fmt or self.fmt
         groups = self.k // 128
-        if self.fmt == "w8":
+        if fmt == "w8":
             return self.n * self.k + 2 * self.n
-        if self.fmt == "w4_ref":
+        if fmt == "w4_ref":
             return self.n * self.k // 2 + 2 * self.n * groups
         return self.n * self.k // 2 + 4 * self.n * groups
 
+    def algorithmic_bytes(self, fmt=None):
+        """Every weight byte once, activations in, outputs out."""
+        n_out = self.n // 2 if self.swiglu else self.n
+        return float(self.weight_bytes(fmt) + 2 * self.m * self.k + 2 * self.m * n_out)
+
     @property
     def bytes(self):
-        """Algorithmic bytes: every weight byte once, activations in, outputs out."""
-        n_out = self.n // 2 if self.swiglu else self.n
-        return float(self.weight_bytes() + 2 * self.m * self.k + 2 * self.m * n_out)
+        return self.algorithmic_bytes()
+
+    def shard(self, world):
+        return Case(self.name, self.fmt, self.m, self.k, self.n // world, self.dtype, self.outliers,
+                    self.swiglu, self.cfg)
 
 
 def build_cases(workload: str, layout: str) -> list[Case]:
     w4 = "w4_asym" if layout == "asym" else "w4_ref"
+    if workload == "all":
+        return [c for part in ("c1", "c2", "c4", "c5") for c in build_cases(part, layout)]
     if workload == "c2":
-        return [Case(name, w4, m, *SHAPES_8B[name], torch.float16)
+        return [Case(name, w4, m, *SHAPES_8B[name], torch.float16, cfg="c2")
                 for name in ("gate_up", "down") for m in (1, 4, 16, 64, 256)]
     if workload == "c5":
-        return [Case(name, w4, 4096, *SHAPES_8B[name], torch.bfloat16, outliers=True)
+        return [Case(name, w4, 4096, *SHAPES_8B[name], torch.bfloat16, outliers=True, cfg="c5")
                 for name in ("gate_up", "down")]
     if workload == "c4":
-        return [Case(name, "w8", m, *SHAPES_8B[name], torch.bfloat16)
+        return [Case(name, "w8", m, *SHAPES_8B[name], torch.bfloat16, cfg="c4")
                 for name in ("q", "kv", "o", "gate_up", "down") for m in (1, 16, 64, 512)]
     if workload == "c1":
-        return [Case("gate_0p6b", "w8", 8, 1024, 3072, torch.float16)]
+        return [Case("gate_0p6b", "w8", 8, 1024, 3072, torch.float16, cfg="c1")]
     if workload == "head":
         # the reference's largest single matrix: the Qwen3-8B output head (4096 -> 151936)
-        return [Case("lm_head", w4, m, 4096, 151936, torch.float16) for m in (1, 16, 256)]
+        return [Case("lm_head", w4, m, 4096, 151936, torch.float16, cfg="head") for m in (1, 16, 256)]
     if workload == "mlp":
         # beyond the reference: gate_proj + up_proj + silu(gate) * up of a Qwen3-8B feed-forward
         # as ONE launch over interleaved quantized rows (2 x 12288 rows of K = 4096)
         k, n = SHAPES_8B["gate_up"]
-        return [Case("gate_up_swiglu", w4, m, k, 2 * n, torch.float16, swiglu=True)
+        return [Case("gate_up_swiglu", w4, m, k, 2 * n, torch.float16, swiglu=True, cfg="mlp")
                 for m in (1, 16, 64, 256, 1024)]
     if workload == "c3":
         # one mixed step of a Qwen3-0.6B-shaped model: 16 decode rows + one 128-token chunk
         shapes = {"q": (1024, 2048), "k": (1024, 1024), "v": (1024, 1024), "o": (2048, 1024),
                   "gate": (1024, 3072), "up": (1024, 3072), "down": (3072, 1024)}
-        return [Case(f"L{layer:02d}.{name}", "w8", 144, k, n, torch.float16)
+        return [Case(f"L{layer:02d}.{name}", "w8", 144, k, n, torch.float16, cfg="c3")
                 for layer in range(28) for name, (k, n) in shapes.items()]
     raise SystemExit(f"unknown workload {workload}")
 
@@ -125,16 +168,16 @@ def peaks() -> dict:
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def roofline_entry(case: Case, seconds: float, pk: dict) -> dict:
-    t_hbm = case.bytes / (pk["hbm_gbs"] * 1e9)
-    t_tc = case.flops / (pk["tflops"] * 1e12)
+def roofline_of(total_bytes: float, total_flops: float, seconds: float, pk: dict) -> dict:
+    """Roofline entry of one launch or of a group of launches (sums in, aggregate out)."""
+    t_hbm = total_bytes / (pk["hbm_gbs"] * 1e9)
+    t_tc = total_flops / (pk["tflops"] * 1e12)
     if t_hbm >= t_tc:
-        achieved, peak, unit, bound = case.bytes / seconds / 1e9, pk["hbm_gbs"], "GB/s", "hbm"
+        achieved, peak, unit, bound = total_bytes / seconds / 1e9, pk["hbm_gbs"], "GB/s", "hbm"
     else:
-        achieved, peak, unit, bound = case.flops / seconds / 1e12, pk["tflops"], "TFLOP/s", "tensor"
+        achieved, peak, unit, bound = total_flops / seconds / 1e12, pk["tflops"], "TFLOP/s", "tensor"
     return {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": unit,
-            "frac": round(achieved / peak, 4), "peak_source": pk["source"],
-            "traffic": NCU_TRAFFIC_BYTES.get(case.key)}
+            "frac": round(achieved / peak, 4), "peak_source": pk["source"]}
 
 
 # --------------------------------------------------------------------------- clocks
@@ -202,32 +245,39 @@ def make_activation(case: Case, seed: int, device) -> torch.Tensor:
     return x.to(case.dtype).to(device)
 
 
-def make_weight_sets(cases: list[Case], copies: int, device, rank: int = 0, world: int = 1):
-    """Quantized weights per (fmt, shape): `copies` distinct buffers each (L2 rotation).
-
-    With world > 1 each rank keeps rows [rank*N/world, (rank+1)*N/world) of every matrix.
-    """
+def quantize_for(case: Case, weight: torch.Tensor) -> tuple:
     from full_inference_engine_b200.kernels import w4a16_format as w4
     from full_inference_engine_b200.kernels import w8a16_linear
 
+    if case.fmt == "w8":
+        return w8a16_linear.quantize_weight_per_channel(weight)
+    if case.fmt == "w4_ref":
+        return w4.quantize_weight_w4_grouped(weight)
+    return w4.quantize_weight_w4_asym(weight)
+
+
+def make_weight_sets(cases: list[Case], copies_of: dict, device, rank: int = 0, world: int = 1,
+                     keep_full: bool = False):
+    """Quantized weights per (fmt, name): ``copies_of[key]`` distinct buffers each (L2 rotation).
+
+    With world > 1 each rank keeps rows [rank*N/world, (rank+1)*N/world) of every matrix;
+    ``keep_full`` also returns the whole quantized matrix per key (for the gather parity check).
+    """
     sets: dict[tuple, list] = {}
+    full: dict[tuple, tuple] = {}
     for case in cases:
-        key = (case.fmt, case.name)
+        key = case.wkey
         if key in sets:
             continue
         gen = torch.Generator(device=device).manual_seed(1000 + len(sets))
         weight = torch.randn(case.n, case.k, generator=gen, device=device) * 0.02
+        if keep_full and world > 1:
+            full[key] = quantize_for(case, weight)
         rows = case.n // world
-        weight = weight[rank * rows:(rank + 1) * rows]
-        if case.fmt == "w8":
-            first = w8a16_linear.quantize_weight_per_channel(weight)
-        elif case.fmt == "w4_ref":
-            first = w4.quantize_weight_w4_grouped(weight)
-        else:
-            first = w4.quantize_weight_w4_asym(weight)
+        first = quantize_for(case, weight[rank * rows:(rank + 1) * rows])
         del weight
-        sets[key] = [first] + [tuple(t.clone() for t in first) for _ in range(copies - 1)]
-    return sets
+        sets[key] = [first] + [tuple(t.clone() for t in first) for _ in range(copies_of[key] - 1)]
+    return sets, full
 
 
 def forward(case: Case, x: torch.Tensor, weights: tuple) -> torch.Tensor:
@@ -251,7 +301,36 @@ def unfused_forward(case: Case, x: torch.Tensor, halves: tuple) -> torch.Tensor:
     return swiglu.swiglu_reference(forward(plain, x, halves[0]), forward(plain, x, halves[1]))
 
 
+def kernel_of(case: Case) -> str:
+    """The kernel instantiation (and tiling) that serves this case on the current device."""
+    from full_inference_engine_b200 import _lib
+
+    layout = _lib.W4_ASYM_ZP_INT32 if case.fmt == "w4_asym" else _lib.W4_REF_SPLIT_HALF_SYM
+    return _lib.describe_plan(8 if case.fmt == "w8" else 4, case.m, case.n, case.k, layout)
+
+
+def time_graph(graph, reps: int, rounds: int = 7) -> float:
+    """Median seconds per launch of a graph holding `reps` launches."""
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(rounds):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e) / reps)
+    return statistics.median(times) * 1e-3
+
+
 # --------------------------------------------------------------------------- CPU path
+def cpu_fmt(case: Case) -> str:
+    """The layout the reference's CPU path reads: its own split-half INT4, or int8."""
+    return "w8" if case.fmt == "w8" else "w4_ref"
+
+
 def cpu_inputs(cases: list[Case]):
     """Host tensors for the reference's CPU path (quantized with the CPU oracle)."""
     import numpy as np
@@ -260,7 +339,7 @@ def cpu_inputs(cases: list[Case]):
 
     weights, acts = {}, {}
     for i, case in enumerate(cases):
-        key = (case.fmt, case.name)
+        key = case.wkey
         if key not in weights:
             gen = torch.Generator().manual_seed(1000 + len(weights))
             w = (torch.randn(case.n, case.k, generator=gen) * 0.02).numpy()
@@ -274,29 +353,59 @@ def cpu_inputs(cases: list[Case]):
     return weights, acts
 
 
-def cpu_step(cases, weights, acts, limit=None):
+def cpu_step(cases, weights, acts):
     from oracle import cpu_path
 
-    done = 0
     for i, case in enumerate(cases):
-        if limit is not None and i not in limit:
-            continue
-        w = weights[(case.fmt, case.name)]
+        w = weights[case.wkey]
         if case.swiglu:
             cpu_path.gate_up_swiglu_forward(acts[i], w[0], w[1], int8=case.fmt == "w8")
         elif case.fmt == "w8":
             cpu_path.int8linear_forward(acts[i], w[0], w[1])
         else:
             cpu_path.w4a16_dense_forward(acts[i], w[0], w[1])
-        done += 1
-    return done
+
+
+def cpu_split(cases, weights, acts) -> dict:
+    """Dequantise-only and matmul-only times of the CPU path, one representative case per
+    format (the reference's own split, benchmarks/kernels/w4a16_bench.py:82-90)."""
+    from torch.nn import functional as F
+
+    from oracle import cpu_path
+
+    out = {}
+    for fmt in ("w4", "w8"):
+        pick = [i for i, c in enumerate(cases) if (c.fmt == "w8") == (fmt == "w8") and not c.swiglu]
+        if not pick:
+            continue
+        # the case closest to M = 16 of the widest matrix
+        i = min(pick, key=lambda j: (-cases[j].n * cases[j].k, abs(cases[j].m - 16)))
+        case, w, x = cases[i], weights[cases[i].wkey], acts[i]
+
+        def dequant():
+            if fmt == "w8":
+                return w[0].to(dtype=x.dtype) * w[1].to(dtype=x.dtype)[:, None]
+            return cpu_path.unpack_w4(w[0], w[1], case.k).to(x.dtype)
+
+        dense = dequant()
+        td, tm = [], []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            dequant()
+            td.append(time.perf_counter() - t0)
+            t0 = time.perf_counter()
+            F.linear(x, dense)
+            tm.append(time.perf_counter() - t0)
+        out[fmt] = {"case": f"{cpu_fmt(case)}:{case.name}:M{case.m}",
+                    "dequant_only_ms": round(statistics.median(td) * 1e3, 2),
+                    "matmul_only_ms": round(statistics.median(tm) * 1e3, 2)}
+    return out
 
 
 def time_cpu(cases, budget_s: float = 20.0, min_steps: int = 2):
-    """(seconds per step, steps timed, cores, sample description) on a bounded sample."""
+    """(seconds per step, steps timed, cores, sample description, split) on a bounded sample."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    # keep the sample bounded: the M=4096 cases are sampled as they are, but only one pass
     weights, acts = cpu_inputs(cases)
     t0 = time.perf_counter()
     cpu_step(cases, weights, acts)                       # warm-up pass
@@ -311,8 +420,12 @@ def time_cpu(cases, budget_s: float = 20.0, min_steps: int = 2):
         times.append(time.perf_counter() - t0)
     sample = (f"all {len(cases)} cases of the workload, {steps} timed passes after 1 warm-up, "
               f"torch CPU ops on {cores} threads; INT4 cases use the reference's own "
-              f"split-half layout")
-    return statistics.median(times), steps, cores, sample
+              f"split-half layout (bytes counted for that layout)")
+    return statistics.median(times), steps, cores, sample, cpu_split(cases, weights, acts)
+
+
+def cpu_bytes(cases) -> float:
+    return sum(c.algorithmic_bytes(cpu_fmt(c)) for c in cases)
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -335,20 +448,21 @@ def run_reference(args, cases):
         if time.perf_counter() - start > t_budget:
             break
     sec = sum(times) / len(times)
-    total_bytes = sum(c.bytes for c in cases)
+    total_bytes = cpu_bytes(cases)
     total_flops = sum(c.flops for c in cases)
     value = total_bytes / sec / 1e9
     sample = (f"{len(times)} of {args.steps} requested passes over all {len(cases)} cases "
               f"(bounded to {t_budget:.0f} s), torch CPU dequantise + F.linear on {cores} threads; "
-              "the oracle's port of the reference CPU path (the reference tree is not on this box)")
+              "the oracle's port of the reference CPU path (the reference tree is not on this box); "
+              "INT4 in the reference's split-half layout, bytes counted for that layout")
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "GB/s",
         "tflops": round(total_flops / sec / 1e12, 5), "n_gpus": args.gpus, "steps": len(times),
         "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16/bf16 activations, fp32 accumulate",
-        "data": "synthetic", "config": config_dict(args, cases, rotation=None),
+        "data": "synthetic", "config": config_dict(args, cases),
         "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": sample},
+                         "sample": sample, "split": cpu_split(cases, weights, acts)},
         "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -356,30 +470,23 @@ def run_reference(args, cases):
     print(json.dumps(line), flush=True)
 
 
-def config_dict(args, cases, rotation):
+def config_dict(args, cases):
+    """The same dictionary on both arms: it names the work, not how an arm ran it."""
+    int4 = any(c.fmt != "w8" for c in cases)
     return {
-        "workload": {"c2": "config 2: INT4 g128 M-sweep {1,4,16,64,256} at Qwen3-8B gate/up "
-                           "(4096->12288) and down (12288->4096), fp16 activations",
-                     "c5": "config 5: INT4 g128 prefill M=4096 bf16 with 1% outlier rows, "
-                           "gate/up and down",
-                     "c4": "config 4: W8A16 bf16 at Qwen3-8B q/kv/o/gate_up/down, M in {1,16,64,512}",
-                     "c1": "config 1: W8A16 M=8 K=1024 N=3072 fp16",
-                     "head": "the Qwen3-8B output head, INT4 g128 4096 -> 151936 (the reference's largest "
-                             "matrix, benchmarks/kernels/w4a16_bench.py), M in {1,16,256}, fp16",
-                     "mlp": "beyond the reference: INT4 g128 gate_proj + up_proj + silu(gate) * up of a "
-                            "Qwen3-8B feed-forward (K=4096, 2 x 12288 interleaved rows) in one launch, "
-                            "M in {1,16,64,256,1024}, fp16; per_case carries the two-projections-plus-"
-                            "elementwise time beside it",
-                     "c3": "config 3: 28 x 7 random-init Qwen3-0.6B W8A16 projections, one mixed "
-                           "step of M=144 rows (16 decode + 128 prefill), fp16, one CUDA graph"}[args.workload],
-        "layout": {"asym": "asymmetric int32 x8 nibbles + fp16 scale and zero-point",
-                   "ref": "reference split-half uint8 + fp16 scale"}[args.layout]
-        if cases[0].fmt != "w8" else "int8 per-channel fp16 scale",
+        "workload": WORKLOAD_TEXT[args.workload],
+        "layout": ("INT4: the B200 arm reads "
+                   + ("the asymmetric layout (int32 x8 nibbles + fp16 scale and zero-point)"
+                      if args.layout == "asym" else "the reference's split-half uint8 + fp16 scale layout")
+                   + "; the reference arm always reads the reference's split-half layout (its only one)"
+                   if int4 else "") + ("; " if int4 and any(c.fmt == "w8" for c in cases) else "")
+        + ("W8: int8 per-channel, fp16 scale" if any(c.fmt == "w8" for c in cases) else ""),
         "cases": len(cases),
         "parallelism": (f"N-sharded x{args.gpus}, all-gather "
                         + ("fused into the kernel epilogue (peer stores over NVLink)"
                            if args.gather == "fused" else "by NCCL")) if args.gpus > 1 else "single GPU",
-        "l2": rotation,
+        "l2": "inputs larger than L2: every launch reads its own weight buffer and step variants "
+              "alternate, so that at least 2 x 126 MiB of distinct weights pass between two uses of a buffer",
     }
 
 
@@ -421,23 +528,39 @@ def run_b200(args, cases):
             print(f"# rank {rank}: {msg}", file=sys.stderr, flush=True)
 
     pk = peaks()
-    copies = {"c1": 48, "c2": 10, "c3": 1, "c4": 4, "c5": 6, "mlp": 6, "head": 2}[args.workload]
-    weight_sets = make_weight_sets(cases, copies, device, rank, world)
+    local_cases = [c.shard(world) for c in cases]
+    # Every case of a step reads its own buffer of its matrix; `variants` step variants use
+    # disjoint buffers, enough of them that >= 2 x L2 of distinct weights pass between two uses
+    # of the same buffer.
+    uses: dict[tuple, int] = {}
+    use_index = []
+    for c in local_cases:
+        use_index.append(uses.get(c.wkey, 0))
+        uses[c.wkey] = use_index[-1] + 1
+    step_weight_bytes = sum(c.weight_bytes() for c in local_cases)
+    variants = max(2, min(96, -(-2 * L2_BYTES // step_weight_bytes)))
+    if args.workload == "c3":
+        variants = 1          # 196 distinct matrices, 600 MB per step
+    copies_of = {key: n * variants for key, n in uses.items()}
+    weight_sets, full_sets = make_weight_sets(cases, copies_of, device, rank, world, keep_full=True)
     acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
-    # per-rank view of each case
-    local_cases = [Case(c.name, c.fmt, c.m, c.k, c.n // world, c.dtype, c.outliers, c.swiglu) for c in cases]
+
+    def weights_of(i, variant):
+        case = local_cases[i]
+        return weight_sets[case.wkey][use_index[i] + variant * uses[case.wkey]]
+
     gathered = [torch.empty(world, c.m, c.n // world, dtype=c.dtype, device=device) if world > 1 else None
                 for c in cases]
     # fused all-gather: full [M, N] outputs in symmetric memory, written by every rank's epilogue
     fused_out = None
-    if world > 1 and args.gather == "fused":
+    if world > 1:
         from full_inference_engine_b200.quantization.sharded import SymmetricOutput
 
         fused_out = [SymmetricOutput(c.m, c.n, c.dtype, device) for c in cases]
 
-    def forward_gather(i, case, x, w):
-        """This rank's columns of case i delivered to every rank; returns the local view."""
-        if fused_out is not None:
+    def forward_gather(i, case, x, w, how):
+        """This rank's columns of case i delivered to every rank; returns the full [M, N] view."""
+        if how == "fused":
             from full_inference_engine_b200.quantization.sharded import fused_forward_gather
 
             if case.fmt == "w8":
@@ -450,42 +573,55 @@ def run_b200(args, cases):
                 return fused_out[i].tensor
         y = forward(case, x, w)
         dist.all_gather_into_tensor(gathered[i], y)
-        return y
+        return gathered[i].permute(1, 0, 2).reshape(case.m, -1)
 
-    def one_step(variant: int, gather: bool = True):
+    def one_step(variant: int, how: str):
+        """how: "local" (this rank's GEMMs only), "fused" or "nccl" (GEMM + all-gather)."""
         outs = []
         for i, case in enumerate(local_cases):
-            sets = weight_sets[(case.fmt, case.name)]
-            w = sets[(i + variant * len(local_cases)) % len(sets)]
-            if world > 1 and gather:
-                y = forward_gather(i, case, acts[i], w)
+            w = weights_of(i, variant)
+            if world > 1 and how != "local":
+                outs.append(forward_gather(i, case, acts[i], w, how))
             else:
-                y = forward(case, acts[i], w)
-            outs.append(y)
+                outs.append(forward(case, acts[i], w))
         return outs
 
-    step_weight_bytes = sum(c.weight_bytes() for c in local_cases)
-    # enough step variants (each on its own weight copies) that >= 2 x L2 of distinct weights
-    # pass between two uses of the same buffer
-    variants = max(1, min(copies, -(-2 * L2_BYTES // step_weight_bytes)))
-    if copies > 1:
-        variants = max(2, variants)
-    rotation = (f"inputs larger than L2: each case reads its own weight buffer and {variants} step "
-                f"variant(s) alternate, {variants * step_weight_bytes / 2**20:.0f} MiB of distinct "
-                f"weights between reuses (L2 = 126 MiB)")
+    default_how = "local" if world == 1 else args.gather
 
-    # eager warm-up (also sizes the workspace), then capture two step variants
+    # eager warm-up (also sizes the workspace)
     note("inputs ready")
     for v in range(variants):
-        one_step(v)
+        one_step(v, default_how)
     torch.cuda.synchronize()
     note("eager warm-up done")
 
-    # ---- end to end (measured before any graph holds NCCL work): pinned host activations in, host results out, through the public API
+    # ---- multi-rank only: every case's gathered output against this rank's own single-GPU
+    # forward of the whole matrix, once, outside every timed region
+    gather_parity = None
+    if world > 1:
+        worst, bad = 0.0, []
+        for how in ("fused", "nccl"):
+            for i, case in enumerate(local_cases):
+                got = forward_gather(i, case, acts[i], weights_of(i, 0), how).float()
+                want = forward(cases[i], acts[i], full_sets[cases[i].wkey]).float()
+                rel = float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+                worst = max(worst, rel)
+                if not rel <= 1e-2:
+                    bad.append(f"{how}:{cases[i].key}:{rel:.3e}")
+                torch.cuda.synchronize()
+        flag = torch.tensor([worst, float(len(bad))], dtype=torch.float64)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=cpu_group)
+        gather_parity = {"max_rel_err": float(flag[0]), "ok": float(flag[1]) == 0.0,
+                         "cases": 2 * len(cases), "bar": 1e-2,
+                         "against": "this rank's single-GPU forward of the whole matrix",
+                         "failed_on_rank0": bad}
+        del full_sets
+        note(f"gather parity: {gather_parity}")
+
+    # ---- end to end (measured before any graph holds NCCL work): pinned host activations in,
+    # host results out, through the public API
     host_x = [torch.empty(c.m, c.k, dtype=c.dtype).pin_memory().copy_(acts[i].cpu()) for i, c in enumerate(cases)]
-    host_y = [torch.empty(c.m, (c.n if fused_out is not None else c.n // world) // (2 if c.swiglu else 1),
-                          dtype=c.dtype).pin_memory()
-              for c in cases]
+    host_y = [torch.empty(c.m, c.n // (2 if c.swiglu else 1), dtype=c.dtype).pin_memory() for c in cases]
     dev_x = [torch.empty_like(a) for a in acts]
 
     # Three streams per step: activations in, projections, results out.  A projection waits only
@@ -507,9 +643,8 @@ def run_b200(args, cases):
                 arrived = torch.cuda.Event()
                 arrived.record(copy_in)
             main.wait_event(arrived)
-            sets = weight_sets[(case.fmt, case.name)]
-            w = sets[(i + variant * len(local_cases)) % len(sets)]
-            y = forward_gather(i, case, dev_x[i], w) if world > 1 else forward(case, dev_x[i], w)
+            w = weights_of(i, variant)
+            y = forward_gather(i, case, dev_x[i], w, args.gather) if world > 1 else forward(case, dev_x[i], w)
             computed = torch.cuda.Event()
             computed.record(main)
             with torch.cuda.stream(copy_out):
@@ -522,12 +657,13 @@ def run_b200(args, cases):
     # The user-level call pattern of the reference engine: the step (staging copy in, every
     # projection, copy out) is captured once per variant and replayed; each timed step is
     # replay + synchronise + a host read of the result.
-    for v in range(variants):
+    e2e_variants = min(variants, 4)
+    for v in range(e2e_variants):
         e2e_enqueue(v)
     torch.cuda.synchronize()
     e2e_graphs = []
     try:
-        for v in range(variants):
+        for v in range(e2e_variants):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 e2e_enqueue(v)
@@ -546,28 +682,33 @@ def run_b200(args, cases):
         return float(host_y[-1][0, 0])
 
     for j in range(3):
-        e2e_step(j % variants)
+        e2e_step(j % e2e_variants)
     barrier()
     e2e_steps = max(3, min(args.steps, 50))
     t0 = time.perf_counter()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     for j in range(e2e_steps):
-        e2e_step(j % variants)
+        e2e_step(j % e2e_variants)
     e.record()
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks(max(s.elapsed_time(e), (time.perf_counter() - t0) * 1e3) / e2e_steps)
     note(f"e2e done: {e2e_ms:.4f} ms/step")
+    del e2e_graphs
 
-    launches_before = _lib.launch_count()
-    graphs = []
-    use_graph = True
-    try:
+    def capture_steps(how):
+        graphs = []
         for v in range(variants):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                one_step(v)
+                one_step(v, how)
             graphs.append(g)
+        return graphs
+
+    launches_before = _lib.launch_count()
+    use_graph = True
+    try:
+        graphs = capture_steps(default_how)
     except Exception as exc:      # NCCL capture unsupported etc.: time eager launches instead
         use_graph = False
         graphs = []
@@ -581,15 +722,15 @@ def run_b200(args, cases):
         if use_graph:
             graphs[i % variants].replay()
         else:
-            one_step(i % variants)
+            one_step(i % variants, default_how)
 
     sampler = ClockSampler(local)
     sampler.start()
     # bring the clocks up, then the requested warm-up steps.  A FIXED count: with more than
     # one rank every rank must issue the same number of collectives.
-    for i in range(256):
+    for i in range(64):
         run_step(i)
-        if i % 64 == 63:
+        if i % 16 == 15:
             torch.cuda.synchronize()
     for j in range(max(3, args.warmup)):
         run_step(j)
@@ -607,69 +748,87 @@ def run_b200(args, cases):
     ms_step = ms_total / args.steps
     note(f"timed region done: {ms_step:.4f} ms/step")
 
-    # ---- multi-rank only: the sharded GEMMs alone (no collective), same protocol, so the
-    # line can show how the compute phase and the gather phase each scale
-    gemm_only_ms = None
+    # ---- multi-rank only: the other phases with the same protocol, so the line can show how
+    # the compute phase and each kind of gather scale
+    phase_ms = {}
     if world > 1:
-        torch.cuda.synchronize()
-        for v in range(variants):
-            one_step(v, gather=False)
-        solo = []
-        for v in range(variants):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                one_step(v, gather=False)
-            solo.append(g)
-        for j in range(16):
-            solo[j % variants].replay()
-        torch.cuda.synchronize()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for j in range(args.steps):
-            solo[j % variants].replay()
-        s1.record()
-        torch.cuda.synchronize()
-        gemm_only_ms = max_over_ranks(s0.elapsed_time(s1) / args.steps)
-        note(f"gemm-only: {gemm_only_ms:.4f} ms/step")
+        phase_ms[args.gather] = ms_step
+        for how in ("local", "fused", "nccl"):
+            if how in phase_ms:
+                continue
+            torch.cuda.synchronize()
+            barrier()
+            try:
+                solo = capture_steps(how)
+            except Exception as exc:
+                torch.cuda.synchronize()
+                note(f"phase {how}: capture failed ({exc})")
+                continue
+            for j in range(16):
+                solo[j % variants].replay()
+            torch.cuda.synchronize()
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for j in range(args.steps):
+                solo[j % variants].replay()
+            s1.record()
+            torch.cuda.synchronize()
+            phase_ms[how] = max_over_ranks(s0.elapsed_time(s1) / args.steps)
+            note(f"phase {how}: {phase_ms[how]:.4f} ms/step")
+            del solo
 
-    # ---- per-case latency (roofline): R back-to-back launches over rotating weight copies
+    # ---- per-case latency (roofline): back-to-back launches over enough distinct weight
+    # buffers that none is still in L2 when it comes round again
     per_case = []
-    # per-case latencies are a single-GPU diagnostic; the multi-rank run reports the step only
-    for i, case in enumerate(local_cases if world == 1 else []):
+    for i, case in enumerate(local_cases):
         if args.workload == "c3":
             if not case.name.startswith("L00."):
                 continue
             # the same projection of all 28 layers: 28 distinct weight buffers in rotation
             suffix = case.name.split(".", 1)[1]
-            sets = [weight_sets[(c.fmt, c.name)][0] for c in local_cases if c.name.endswith("." + suffix)]
+            sets = [weight_sets[c.wkey][0] for c in local_cases if c.name.endswith("." + suffix)]
         else:
-            sets = weight_sets[(case.fmt, case.name)]
+            sets = list(weight_sets[case.wkey])
+            want = max(2, -(-2 * L2_BYTES // max(1, case.weight_bytes())) + 1)
+            want = min(want, 64)
+            while len(sets) < want:
+                sets.append(tuple(t.clone() for t in sets[0]))
         reps = len(sets)
-        for w in sets[:2]:
-            forward(case, acts[i], w)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for w in sets:
-                forward(case, acts[i], w)
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        times = []
-        for _ in range(7):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            g.replay()
-            e.record()
+        entry = {"case": cases[i].key, "config": case.cfg, "M": case.m, "K": case.k, "N": cases[i].n,
+                 "dtype": "fp16" if case.dtype is torch.float16 else "bf16", "kernel": kernel_of(case)}
+        hows = ("local",) if world == 1 else ("local", "fused", "nccl")
+        for how in hows:
+            def launch(w, how=how):
+                if how == "local":
+                    return forward(case, acts[i], w)
+                return forward_gather(i, case, acts[i], w, how)
+
+            for w in sets[:2]:
+                launch(w)
             torch.cuda.synchronize()
-            times.append(s.elapsed_time(e) / reps)
-        sec = statistics.median(times) * 1e-3
-        entry = {"case": case.key, "M": case.m, "K": case.k, "N": case.n, "us": round(sec * 1e6, 2),
-                 "GBps": round(case.bytes / sec / 1e9, 1), "TFLOPs": round(case.flops / sec / 1e12, 2)}
-        entry.update(roofline_entry(case, sec, pk))
-        entry["frac_of_nominal"] = round(
-            max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
-        if args.workload == "head" and case.fmt != "w8":
+            barrier()
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for w in sets:
+                        launch(w)
+            except Exception as exc:
+                torch.cuda.synchronize()
+                note(f"per-case capture failed for {case.key} {how}: {exc}")
+                continue
+            sec = max_over_ranks(time_graph(g, reps))
+            del g
+            if how == "local":
+                entry.update({"us": round(sec * 1e6, 2), "GBps": round(case.bytes / sec / 1e9, 1),
+                              "TFLOPs": round(case.flops / sec / 1e12, 2)})
+                entry.update(roofline_of(case.bytes, case.flops, sec, pk))
+                entry["traffic"] = NCU_TRAFFIC_BYTES.get(case.key) if world == 1 else None
+                entry["frac_of_nominal"] = round(max(case.bytes / 8e12, case.flops / 2.25e15) / sec, 4)
+                entry["_sec"] = sec
+            else:
+                entry[f"{how}_gather_us"] = round(sec * 1e6, 2)
+        if world == 1 and args.workload == "head" and case.fmt != "w8":
             # greedy decoding over the head: projection + torch.argmax against the fused epilogue
             from full_inference_engine_b200.kernels import argmax as fused_argmax
 
@@ -686,20 +845,9 @@ def run_b200(args, cases):
                 with torch.cuda.graph(g3):
                     for w in sets:
                         pick(w, fused)
-                for _ in range(3):
-                    g3.replay()
-                torch.cuda.synchronize()
-                t3 = []
-                for _ in range(7):
-                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    s.record()
-                    g3.replay()
-                    e.record()
-                    torch.cuda.synchronize()
-                    t3.append(s.elapsed_time(e) / reps)
-                entry[label] = round(statistics.median(t3) * 1e3, 2)
+                entry[label] = round(time_graph(g3, reps) * 1e6, 2)
                 del g3
-        if case.swiglu:
+        if world == 1 and case.swiglu:
             # the same work as two projections + an elementwise kernel, same protocol
             halves = [tuple(tuple(t[part::2].contiguous() for t in w) for part in (0, 1)) for w in sets]
             unfused_forward(case, acts[i], halves[0])
@@ -708,21 +856,10 @@ def run_b200(args, cases):
             with torch.cuda.graph(g2):
                 for h in halves:
                     unfused_forward(case, acts[i], h)
-            for _ in range(3):
-                g2.replay()
-            torch.cuda.synchronize()
-            times2 = []
-            for _ in range(7):
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record()
-                g2.replay()
-                e.record()
-                torch.cuda.synchronize()
-                times2.append(s.elapsed_time(e) / reps)
-            entry["unfused_us"] = round(statistics.median(times2) * 1e3, 2)
+            entry["unfused_us"] = round(time_graph(g2, reps) * 1e6, 2)
             del g2, halves
         per_case.append(entry)
-        del g
+        del sets
     clocks = sampler.stop()
     note("per-case timing done")
 
@@ -730,21 +867,61 @@ def run_b200(args, cases):
     if fused_out is not None:      # a bounded wait of the fused gather protocol expired somewhere
         status = status or (7 if any(o.status() for o in fused_out) else 0)
 
+    exit_code = 0
     if rank == 0:
         total_bytes = sum(c.bytes for c in cases)          # whole job, all ranks
         total_flops = sum(c.flops for c in cases)
-        dominant = max(per_case, key=lambda r: r["us"]) if per_case else None
-        step_us = sum(r["us"] for r in per_case) * (28 if args.workload == "c3" else 1)
+        scale = 28 if args.workload == "c3" else 1
+        timed = [r for r in per_case if "_sec" in r]
+        step_sec = sum(r["_sec"] for r in timed) * scale
+
+        def aggregate(rows):
+            """Roofline of a group of launches: per-rank bytes and flops over their summed time."""
+            if not rows:
+                return None
+            by_key = {c.key: lc for c, lc in zip(cases, local_cases)}
+            b = sum(by_key[r["case"]].bytes for r in rows)
+            f = sum(by_key[r["case"]].flops for r in rows)
+            t = sum(r["_sec"] for r in rows)
+            out = roofline_of(b, f, t, pk)
+            out.update({"cases": [r["case"] for r in rows], "us": round(t * 1e6, 2),
+                        "share_of_step": round(t * scale / step_sec, 3) if step_sec else None})
+            return out
+
+        groups: dict[str, list] = {}
+        for r in timed:
+            groups.setdefault(r["kernel"].split(" ")[0], []).append(r)
+        dominant_name = max(groups, key=lambda k: sum(r["_sec"] for r in groups[k])) if groups else None
+        roofline = None
+        if dominant_name:
+            roofline = aggregate(groups[dominant_name])
+            roofline["kernel"] = dominant_name
+            captured = [r for r in groups[dominant_name] if r.get("traffic")]
+            # per launch, like `achieved`: the ncu DRAM byte count of one captured case of this
+            # instantiation (named beside it), or null when none has been captured
+            roofline["traffic"] = captured[0]["traffic"] if captured else None
+            roofline["traffic_case"] = captured[0]["case"] if captured else None
+        by_instantiation = {name: {k: v for k, v in aggregate(rows).items() if k != "cases"} | {"launches": len(rows)}
+                            for name, rows in groups.items()}
+        regimes = {
+            "hbm_M<=16": aggregate([r for r in timed if r["M"] <= 16]),
+            "mid_16<M<2048": aggregate([r for r in timed if 16 < r["M"] < 2048]),
+            "tensor_M>=2048": aggregate([r for r in timed if r["M"] >= 2048]),
+        }
+        for r in per_case:
+            r.pop("_sec", None)
         line = {
             "metric": METRIC, "value": round(total_bytes / (ms_step * 1e-3) / 1e9, 2), "unit": "GB/s",
             "tflops": round(total_flops / (ms_step * 1e-3) / 1e12, 3),
             "n_gpus": args.gpus, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16/bf16 activations, fp32 accumulate", "data": "synthetic",
-            "config": config_dict(args, cases, rotation),
-            "roofline": ({k: dominant[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
-                         | {"kernel": dominant["case"], "share_of_step": round(dominant["us"] / step_us, 3),
-                            "peak_source": pk["source"]}) if dominant else None,
+            "config": config_dict(args, cases),
+            "l2_rotation": f"{variants} step variants, {variants * step_weight_bytes / 2**20:.0f} MiB of "
+                           f"distinct weights per rank between two uses of a buffer (L2 = 126 MiB)",
+            "roofline": roofline,
+            "roofline_by_regime": regimes,
+            "roofline_by_instantiation": by_instantiation,
             "per_case": per_case,
             "clocks": clocks,
             "e2e": {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
@@ -754,60 +931,74 @@ def run_b200(args, cases):
                     "note": "weights stay resident on the device (module state); every step copies the "
                             "activations from pinned host memory, runs every forward and copies the "
                             "results back to pinned host memory (copy-in, compute and copy-out "
-                            "streams overlapped inside one captured graph per step, "
-                            + ("replayed" if e2e_graphs else "eager launches")
-                            + "), then synchronises and reads a result on the host"},
+                            "streams overlapped inside one captured graph per step), then "
+                            "synchronises and reads a result on the host"},
             "gpu_launches": int(launches_per_step * args.steps),
             "timing": "cuda-graph replay" if use_graph else "eager launches",
-            "phases": None if gemm_only_ms is None else {
-                "sharded_gemm_only_ms_per_step": round(gemm_only_ms, 5),
-                "with_all_gather_ms_per_step": round(ms_step, 5)},
+            "phases": None if world == 1 else {
+                "sharded_gemm_only_ms_per_step": round(phase_ms["local"], 5) if "local" in phase_ms else None,
+                "with_fused_all_gather_ms_per_step": round(phase_ms["fused"], 5) if "fused" in phase_ms else None,
+                "with_nccl_all_gather_ms_per_step": round(phase_ms["nccl"], 5) if "nccl" in phase_ms else None,
+                "timed_value_is": args.gather,
+                "per_case": "per_case[*].us is the sharded GEMM alone, fused_gather_us / nccl_gather_us "
+                            "the GEMM with that all-gather"},
+            "gather_parity": gather_parity,
             "device_status": status,
         }
         if world == 1:
-            sec, steps, cores, sample = time_cpu(cases)
-            line["cpu_baseline"] = {"value": round(total_bytes / sec / 1e9, 4), "unit": "GB/s",
+            sec, steps, cores, sample, split = time_cpu(cases)
+            line["cpu_baseline"] = {"value": round(cpu_bytes(cases) / sec / 1e9, 4), "unit": "GB/s",
                                     "cores": cores, "kind": "port", "sample": sample,
-                                    "ms_per_step": round(sec * 1e3, 2)}
+                                    "ms_per_step": round(sec * 1e3, 2), "split": split}
         print(json.dumps(line), flush=True)
+        if gather_parity is not None and not gather_parity["ok"]:
+            exit_code = 3
+        if status:
+            exit_code = exit_code or 4
     if world > 1:
         # leave without further collectives: tear the communicator down from a helper thread
         # and exit even if that blocks (every rank has synchronised its device by now)
+        code = torch.tensor([float(exit_code)], dtype=torch.float64)
+        dist.all_reduce(code, op=dist.ReduceOp.MAX, group=cpu_group)
         torch.cuda.synchronize()
         sys.stdout.flush()
         closer = threading.Thread(target=dist.destroy_process_group, daemon=True)
         closer.start()
         closer.join(timeout=10.0)
-        os._exit(0)
+        os._exit(int(code.item()))
+    if exit_code:
+        sys.exit(exit_code)
 
 
 def run_profile(args, cases):
     """Plain eager launches, one weight buffer per launch: the command ncu wraps."""
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
-    weight_sets = make_weight_sets(cases, 6, device)
+    copies_of = {c.wkey: 6 for c in cases}
+    weight_sets, _ = make_weight_sets(cases, copies_of, device)
     acts = [make_activation(c, 5000 + i, device) for i, c in enumerate(cases)]
     n = 0
     for step in range(max(1, args.warmup) + args.steps):
         for i, case in enumerate(cases):
-            sets = weight_sets[(case.fmt, case.name)]
+            sets = weight_sets[case.wkey]
             forward(case, acts[i], sets[(step + i) % len(sets)])
             n += 1
     torch.cuda.synchronize()
-    print(json.dumps({"profile_launches": n, "cases": [c.key for c in cases]}), flush=True)
+    print(json.dumps({"profile_launches": n, "cases": [c.key for c in cases],
+                      "kernels": sorted({kernel_of(c) for c in cases})}), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "mlp", "head"])
+    ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c4", "c5", "mlp", "head"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="at --gpus > 1: all-gather inside the kernel epilogue, or a NCCL call after it")
+                    help="at --gpus > 1: the all-gather that `value` times (both are reported in `phases`)")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--profile", action="store_true",
                     help="eager launches of the selected cases only (for ncu): no graphs, no e2e, no CPU leg")

@@ -43,6 +43,7 @@ _SIGNATURES = {
                                   _c_void_p, _c_i64, _c_void_p]),
     "b200q_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int]),
     "b200q_workspace_status": (_c_int, [_c_void_p, _c_void_p]),
+    "b200q_describe_plan": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_char_p, _c_size]),
     "b200q_w8a16_forward": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_void_p, _c_int,
                                      _c_void_p, _c_void_p, _c_i64, _c_int, _c_int, _c_int,
                                      _c_void_p, _c_size, _c_int, _c_void_p]),
@@ -169,6 +170,14 @@ def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def workspace_bytes(fmt: int, m: int, n: int, k: int) -> int:
     return int(library().b200q_workspace_bytes(fmt, m, n, k))
+
+
+def describe_plan(fmt: int, m: int, n: int, k: int, layout: int = W4_REF_SPLIT_HALF_SYM,
+                  group: int = 128) -> str:
+    """Kernel instantiation and tiling a plain forward of this geometry takes (diagnostic)."""
+    buf = ctypes.create_string_buffer(256)
+    check(library().b200q_describe_plan(fmt, layout, m, n, k, group, buf, len(buf)), "b200q_describe_plan")
+    return buf.value.decode()
 
 
 def launch_count() -> int:

@@ -124,6 +124,19 @@ size_t b200q_workspace_bytes(int format, int M, int N, int K) {
   return tc_workspace_bytes(format == 8 ? FMT_W8 : FMT_W4_REF, M, N, K);
 }
 
+int b200q_describe_plan(int format, int layout, int M, int N, int K, int group, char* text, size_t size) {
+  if (!text || size == 0) return B200Q_ERR_INVALID;
+  if (format != 8 && format != 4) return B200Q_ERR_INVALID;
+  const int fmt = format == 8 ? FMT_W8 : (layout == B200Q_W4_ASYM_ZP_INT32 ? FMT_W4_ASYM : FMT_W4_REF);
+  const bool tc = format == 8 ? (K % 64 == 0) : (group == 128 && K % 128 == 0);
+  if (!tc || M <= (format == 8 ? kSimtMaxRowsW8 : kSimtMaxRowsW4)) {
+    std::snprintf(text, size, "wq_gemv_simt_kernel<%s>", format == 8 ? "w8" : "w4");
+    return B200Q_OK;
+  }
+  tc_describe_plan(fmt, M, N, K, text, size);
+  return B200Q_OK;
+}
+
 int b200q_workspace_status(const void* workspace, void* stream) {
   if (!workspace) return B200Q_ERR_INVALID;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

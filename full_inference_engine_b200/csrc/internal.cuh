@@ -59,6 +59,7 @@ bool tc_supported(const ForwardArgs& a);
 size_t tc_workspace_bytes(int format, int M, int N, int K);
 int launch_forward_tc(const ForwardArgs& a);
 int tc_output_tiles(int format, int M, int N, int K);
+void tc_describe_plan(int format, int M, int N, int K, char* text, size_t size);
 int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream);
 
 }  // namespace b200q

@@ -165,12 +165,13 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 }
 
 // Instruction descriptor, kind::f16, fp32 accumulate, A and B both K-major.
-// ab_fmt: 0 = f16, 1 = bf16.  M = 128, N = n (multiple of 16, <= 256).
-__host__ __device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t ab_fmt, uint32_t m,
-                                                            uint32_t n) {
+// a_fmt / b_fmt: 0 = f16, 1 = bf16; sm_100a wants the two equal.  M = 128, N = n
+// (multiple of 16, <= 256).
+__host__ __device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t a_fmt, uint32_t b_fmt,
+                                                            uint32_t m, uint32_t n) {
   return (1u << 4)            // D format f32
-         | (ab_fmt << 7)      // A format
-         | (ab_fmt << 10)     // B format
+         | (a_fmt << 7)       // A format
+         | (b_fmt << 10)      // B format
          | ((n >> 3) << 17)   // N
          | ((m >> 4) << 24);  // M
 }

@@ -17,9 +17,10 @@
 
 namespace b200q {
 
-// 64 KiB header (status word, tile counters) + room for the fp32 split-K partials of
-// every geometry whose workspace fits: e.g. M <= 64 at the 4096x12288 / 12288x4096
-// Qwen3-8B shapes.  Larger problems are refused, not truncated.
+// 128 KiB header (status word, tile counters, argmax keys) + room for the fp32 partials of
+// every geometry whose workspace fits: every M <= 64 (the stream-K kernel's partials are
+// bounded by the SM count, not by the matrix), larger M while split-K partials fit.
+// Larger problems are refused, not truncated.
 constexpr size_t kStaticScratchBytes = 16u << 20;
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
@@ -45,15 +46,10 @@ static void* static_scratch_for_current_device(int* status) {
       *status = B200Q_ERR_CUDA;
       return nullptr;
     }
-    // The image zero-fills the array at load; the kernels keep counters and status at
-    // zero between launches.  Clearing the header here makes the starting state
-    // explicit on the first use of a device (a plain memset, nothing is allocated).
-    e = cudaMemset(p, 0, 64 * 1024);
-    if (e != cudaSuccess) {
-      set_last_error("cudaMemset(static scratch header)", e);
-      *status = B200Q_ERR_CUDA;
-      return nullptr;
-    }
+    // Nothing is cleared here: a __device__ array is zero-filled when the library image is
+    // loaded onto the device, and the kernels return counters, keys and the status word to
+    // zero themselves.  (A memset at this point would not be ordered with a forward launched
+    // on a non-blocking stream.)
     ptrs[dev] = p;
   }
   *status = B200Q_OK;

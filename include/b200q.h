@@ -87,9 +87,10 @@ typedef enum b200q_kernel {
  * and then torch.argmax over the [M, vocab] logits).  `y` points at M int64 values; `ldy` is
  * ignored.  Every output is rounded to the activation dtype exactly as the plain call would
  * store it before it is compared, and among equal values the smallest channel wins, so the
- * result equals argmax over the plain call's own output.  One launch: per-row keys live in the
- * workspace (which must be zero before the first call, as for split-K) and the last block of
- * the grid converts them and puts them back to zero.  Tensor-core kernel only; not with
+ * result equals argmax over the plain call's own output.  One launch: per-row keys live in a
+ * region of the workspace that nothing else uses (zero before the first call, like the
+ * counters) and the last block of the grid converts them and puts them back to zero.  At most
+ * 8192 rows per call (B200Q_ERR_UNSUPPORTED beyond).  Tensor-core kernel only; not with
  * SWIGLU_PAIRS, not in the *_forward_gather entry points.                                   */
 #define B200Q_FLAG_ARGMAX 0x400
 
@@ -151,13 +152,26 @@ int b200q_w4_dequant(const void* packed, const void* scales, const void* zeros,
 
 /*
  * Bytes of workspace a forward call of this geometry may use (0 = none).
- * `format`: 8 for W8A16, 4 for either INT4 layout.  The workspace must be
- * zero-filled once when it is allocated; every call leaves it zeroed again
- * where that matters, so graph replays need no memset.  Calls that may overlap
- * on the GPU (different streams) need a workspace each: split-K counters,
- * partials and argmax keys of two running kernels must not share memory.
+ * `format`: 8 for W8A16, 4 for either INT4 layout.  Layout: [0, 256) a status
+ * word, [256, 64 KiB) tile counters, [64 KiB, 128 KiB) the row keys of the fused
+ * argmax, then fp32 partial sums.  The workspace must be zero-filled once when it
+ * is allocated; every call leaves status, counters and keys at zero again, and the
+ * partials are always written before they are read, so graph replays need no
+ * memset and calls of any kind may follow one another on the same workspace.
+ * Calls that may overlap on the GPU (different streams) need a workspace each:
+ * counters, partials and keys of two running kernels must not share memory.
+ * A call with B200Q_FLAG_ARGMAX needs only the first 128 KiB.
  */
 size_t b200q_workspace_bytes(int format, int M, int N, int K);
+
+/*
+ * One line of text naming the kernel instantiation and tiling that a plain forward of
+ * this geometry takes on the current device with B200Q_KERNEL_AUTO ("wq_gemm_sk_kernel<w4_asym>
+ * tok=16 ...").  Host-only diagnostic, no reference counterpart; `layout` and `group` are
+ * ignored for format 8.
+ */
+int b200q_describe_plan(int format, int layout, int M, int N, int K, int group,
+                        char* text, size_t size);
 
 /*
  * Wait for `stream`, then read the status word a forward call keeps at the
@@ -274,9 +288,10 @@ int b200q_gather_wait(const b200q_gather* gather, int tiles_per_rank, void* stre
  *
  *  - Geometries whose b200q_workspace_bytes() exceeds the array are refused with
  *    B200Q_ERR_WORKSPACE (b200q_last_error() names both sizes).
- *  - The first call on each device looks up the array's device address and clears
- *    its 64 KiB header with a synchronous cudaMemset: make that first call before
- *    starting any stream capture on that device.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress): make that first call before starting any stream
+ *    capture on that device.  Nothing is cleared: the array is zero when the library
+ *    image is loaded and the kernels return its counters to zero themselves.
  *  - All calls on a device share the one array and it keeps what the last call
  *    left in it (the kernels return its counters to zero themselves).  Calls that
  *    overlap on the GPU — different streams, or b200q_w4a16_forward given this same

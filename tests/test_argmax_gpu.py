@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+from full_inference_engine_b200 import _lib
 from full_inference_engine_b200.kernels import argmax, w4a16_format as w4, w4a16_linear, w8a16_linear
 from oracle import wq_oracle as oracle
 from tests.helpers import to_np
@@ -90,3 +91,56 @@ def test_module_argmax_matches_forward_argmax():
     assert torch.equal(head.argmax(x), head(x).argmax(dim=-1))
     head.reference = True
     assert head.argmax(x).shape == (2, 5)
+
+
+def _partials_region(ws: torch.Tensor) -> torch.Tensor:
+    return ws[128 * 1024:]
+
+
+@pytest.mark.parametrize("m,k,n", [(16, 12288, 4096), (144, 12288, 1024)])
+def test_argmax_after_a_forward_that_left_partials_in_the_shared_workspace(m, k, n):
+    """A decode step runs projections whose K is split (fp32 partials stay behind in the
+    workspace) and then the head's argmax on the SAME workspace: the keys have a region of
+    their own, so leftovers can never be taken for keys."""
+    torch.manual_seed(1)
+    device = torch.device("cuda", torch.cuda.current_device())
+    packed, scales = w4.quantize_weight_w4_grouped(torch.randn(n, k, device=DEV) * 0.02)
+    x = torch.randn(m, k, device=DEV).half()
+    w4a16_linear.w4a16_linear(x, packed, scales)
+    ws = _lib.workspace_for(device, 256)
+    torch.cuda.synchronize()
+    assert bool((_partials_region(ws) != 0).any()), "the split path did not go through the workspace"
+    head_k, vocab = 1024, 5000
+    hp, hs = w4.quantize_weight_w4_grouped(torch.randn(vocab, head_k, device=DEV) * 0.05)
+    hx = torch.randn(m, head_k, device=DEV).half()
+    dense = w4a16_linear.w4a16_linear(hx, hp, hs)
+    channels = argmax.w4a16_linear_argmax(hx, hp, hs)
+    truth = oracle.linear_fp32(to_np(hx).astype(np.float32), oracle.unpack_w4(to_np(hp), to_np(hs), head_k))
+    _check(channels, dense, truth)
+    assert int(channels.max()) < vocab
+
+
+def test_whole_model_decode_step_then_head_argmax():
+    """install_w4a16 on a two-layer Qwen3, one forward (its projections split K and leave
+    partials in the shared workspace), then the quantized head's fused argmax over the final
+    hidden states: equal to argmax over the model's own logits."""
+    from transformers import AutoModelForCausalLM, Qwen3Config
+
+    from full_inference_engine_b200.quantization import W4A16Linear, install_w4a16
+
+    cfg = Qwen3Config(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=256,
+                      tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float16).eval().cuda()
+    install_w4a16(model, group_size=128)
+    head = model.lm_head
+    assert isinstance(head, W4A16Linear)
+    for tokens in (1, 9, 80):
+        ids = torch.randint(0, 512, (1, tokens), device=DEV)
+        with torch.no_grad():
+            hidden = model.model(input_ids=ids, use_cache=False).last_hidden_state
+            logits = head(hidden)
+            picked = head.argmax(hidden)
+        assert torch.equal(picked, logits.argmax(dim=-1))
+        assert int(picked.max()) < 512
