@@ -19,7 +19,7 @@ LIB_PATH = os.path.join(PACKAGE_DIR, "lib", "libb200q.so")
 # enums of include/b200q.h
 F16, BF16, F32 = 0, 1, 2
 W4_REF_SPLIT_HALF_SYM, W4_ASYM_ZP_INT32 = 0, 1
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC = 0, 1, 2
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC, KERNEL_STREAMK = 0, 1, 2, 3
 FLAG_STATIC_WEIGHTS = 0x100
 FLAG_SWIGLU_PAIRS = 0x200
 FLAG_ARGMAX = 0x400

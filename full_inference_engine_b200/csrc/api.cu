@@ -47,11 +47,17 @@ static int run_forward(ForwardArgs& a, int kernel_and_flags) {
   }
   if (a.swiglu) {
     // the gated-pair epilogue exists in the tensor-core kernel only
-    if (kernel != B200Q_KERNEL_AUTO && kernel != B200Q_KERNEL_TC) return B200Q_ERR_UNSUPPORTED;
+    if (kernel != B200Q_KERNEL_AUTO && kernel != B200Q_KERNEL_TC && kernel != B200Q_KERNEL_STREAMK)
+      return B200Q_ERR_UNSUPPORTED;
+    a.force_streamk = kernel == B200Q_KERNEL_STREAMK;
     return launch_forward_tc(a);
   }
   if (kernel == B200Q_KERNEL_SIMT) return launch_forward_simt(a);
   if (kernel == B200Q_KERNEL_TC) return launch_forward_tc(a);
+  if (kernel == B200Q_KERNEL_STREAMK) {
+    a.force_streamk = true;
+    return launch_forward_tc(a);
+  }
   if (kernel != B200Q_KERNEL_AUTO) return B200Q_ERR_INVALID;
   const int simt_rows = a.format == FMT_W8 ? kSimtMaxRowsW8 : kSimtMaxRowsW4;
   if (a.M <= simt_rows || !tc_supported(a)) return launch_forward_simt(a);

@@ -5,10 +5,14 @@
 // owns the contiguous unit range [b U / G, (b + 1) U / G) in (tile, K block) order, so every
 // block streams the same number of weight bytes whatever the shape: there is no tail wave and
 // no split-K plan.  A run of a block's units inside one tile is a SEGMENT; a segment that
-// covers the tile's whole K is stored directly, otherwise it is an fp32 partial in the
-// workspace and the last contributor to arrive (a counter per tile) sums the tile's partials
-// in block order — fixed order, so results are reproducible — and stores it.  No block ever
-// waits for another block.
+// covers the tile's whole K is stored directly.  Otherwise the first block of the tile (the
+// one whose range ENDS in it, so it gets there last) owns the output: it adds the partials of
+// the tile's other blocks to its own accumulator in block order — fixed order, so results are
+// reproducible — and stores.  The others park their fp32 partials in the workspace as
+// self-validating words (a word of 0 means "not written"), which the owner polls directly:
+// no fence, no flag, no atomic, because under a saturated memory system every dependent trip
+// to L2 costs about a microsecond.  An owner only ever waits for higher-numbered blocks of its
+// own grid (bounded), and the grid is at most one block per SM, so they are resident.
 //
 // A block uses at most half of an SM (448 threads, <= 72 registers, <= 113 KB of shared
 // memory when the ring allows it, 256 TMEM columns), so the NEXT kernel of the stream
@@ -24,8 +28,8 @@
 //                groups already unpack them into tensor memory; only the activations wait
 //   warp 1       TMEM allocation, tcgen05.mma issue (one elected thread), commits
 //   warps 2-5    epilogue: tcgen05.ld of a finished segment (the accumulator is handed back
-//                to the MMA warp as soon as it is in registers), scale/bias, stores or the
-//                partial + last-arriver reduction
+//                to the MMA warp as soon as it is in registers), then park the partial, or
+//                collect the other blocks' partials, scale/bias and store
 //   warps 6-13   two dequantise groups of four warps; a group takes every other unit, each
 //                thread one output channel (its TMEM lane) x the unit's 128 K: packed row out
 //                of shared memory, unpack in registers, A operand (activation dtype) into tensor memory
@@ -53,7 +57,12 @@ constexpr int kSkMaxTok = 64;
 constexpr int kSkTmemCols = 256;                               // accumulator [0, 64), operand stages [64, 256)
 constexpr int kSkACol0 = 64;
 constexpr int kSkBarrierBytes = 512;
-constexpr int kSkMaxGrid = 160;                                // bound used to size the workspace
+static_assert(8 * (2 * kSkMaxStages + 2 * kSkXStages + 2 * kSkSStages + 2 * kSkAStages + 3) + 16 <= kSkBarrierBytes,
+              "the barrier region holds every ring's barriers");
+static_assert(kSkACol0 + 64 * kSkAStages <= kSkTmemCols, "operand stages fit the tensor memory allocation");
+constexpr int kSkMaxGrid = 160;                                // blocks the exchange region has slots for
+static_assert(static_cast<size_t>(kSkMaxGrid) * kSkMaxTok * kBlockN * sizeof(uint32_t) <= kWsExchangeBytes,
+              "the exchange region holds one partial per block");
 constexpr size_t kSkHalfSm = 115712;                           // (228 KiB - 2 x 1 KiB reserved) / 2
 constexpr size_t kSkFullSm = 226 * 1024;
 constexpr int kSkChunkBytes = kBlockN * 16;                    // eight fp16 group parameters of 128 rows
@@ -72,8 +81,7 @@ struct SkParams {
   uint32_t idesc;
   int static_weights;
   int swiglu;
-  float* partial;        // [grid][2][tok][128] fp32
-  unsigned* counters;    // one per weight tile, zero between launches
+  uint32_t* exchange;    // [grid][tok][128] encoded fp32 partials, all zero between launches
   unsigned* status;
 };
 
@@ -85,15 +93,48 @@ __device__ __forceinline__ uint32_t sk_first_unit(uint32_t block, uint32_t grid,
   return static_cast<uint32_t>(static_cast<uint64_t>(block) * units / grid);
 }
 
-// 16 consecutive 32-bit columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+// Partials travel between blocks as self-validating words: an fp32 value v is stored as
+// bits(v + 0.0f) ^ 0x80000000, which is never 0 (v + 0.0f turns -0.0 into +0.0, so the only
+// pattern that would map to 0 cannot occur), and 0 means "not written yet".  The reader polls
+// the data itself, so the writer needs no fence and no flag, and puts the word back to 0.
+__device__ __forceinline__ uint32_t sk_encode(float v) { return __float_as_uint(v + 0.0f) ^ 0x80000000u; }
+__device__ __forceinline__ float sk_decode(uint32_t w) { return __uint_as_float(w ^ 0x80000000u); }
+constexpr uint32_t kSkExchangePolls = 1u << 15;          // x ~1 us per look: gives up after tens of milliseconds
+__device__ __forceinline__ uint32_t ld_relaxed_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Untiled bulk copy global -> shared of this block (both 16-byte aligned, size a multiple of
+// 16 bytes), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// AND of a predicate over the 128 epilogue threads (named barrier 1).
+__device__ __forceinline__ bool epilogue_all(bool mine) {
+  uint32_t out;
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "bar.red.and.pred p, 1, 128, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(mine))
       : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 template <int FMT, typename T>
@@ -123,13 +164,12 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const uint32_t a_empty = a_full + 8 * kSkAStages;                // MMA commit
   const uint32_t acc_full = a_empty + 8 * kSkAStages;              // MMA commit
   const uint32_t acc_empty = acc_full + 8;                         // 4 arrivals: the epilogue warps
-  const uint32_t tmem_slot = acc_empty + 8;
+  const uint32_t xg_full = acc_empty + 8;                          // staged partials of other blocks landed
+  const uint32_t tmem_slot = xg_full + 8;
   const uint32_t abort_slot = tmem_slot + 4;
-  const uint32_t last_slot = abort_slot + 4;
   uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(generic_base + (tmem_slot - smem_base));
   volatile int* abort_p = reinterpret_cast<volatile int*>(generic_base + (abort_slot - smem_base));
-  volatile int* last_p = reinterpret_cast<volatile int*>(generic_base + (last_slot - smem_base));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -161,8 +201,8 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     if (lane == 0) {
       mbar_init(acc_full, 1);
       mbar_init(acc_empty, 4);
+      mbar_init(xg_full, 1);
       *abort_p = 0;
-      *last_p = 0;
       tma_prefetch_desc(&tm_w);
       tma_prefetch_desc(&tm_x);
       if (kGroups) tma_prefetch_desc(&tm_s);
@@ -324,13 +364,12 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     grid_dependency_wait();              // outputs and the workspace belong to the stream order
     const int quarter = warp & 3;        // TMEM lanes this warp may read
     const int ch = quarter * 32 + lane;  // channel inside the tile
-    const int et = threadIdx.x - 64;     // 0..127 among the epilogue threads
     const uint32_t acc_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const int rows = min(p.tok, p.M);
     T* const y = static_cast<T*>(p.y);
     bool ok = true;
     int tile = tile0, kb = kbi0, left = n_units;
-    uint32_t seg_u = u0, acc_phase = 0;
+    uint32_t acc_phase = 0, xg_phase = 0;
     // one finished fp32 value of this thread's channel -> the output (all lanes take part)
     auto emit = [&](int m, int n, float v) {
       if (p.swiglu) {
@@ -344,95 +383,168 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     while (left > 0) {
       const int len = min(left, KB - kb);
       const int n = tile * kBlockN + ch;
-      const bool whole = len == KB;                 // the segment is the tile's whole K
+      // Who else works on this tile: blocks b_lo .. b_hi in unit order.  b_lo (for which the
+      // tile is the END of its range, so it finishes it last) owns the tile's output and adds
+      // the others' partials in block order; every other block parks its partial in its own
+      // exchange slot (a block contributes to at most one tile it does not own: the one under
+      // way at the start of its range).
+      const uint32_t first = static_cast<uint32_t>(tile) * KB;
+      const uint32_t b_lo = (len == KB) ? blockIdx.x : sk_owner(first, G, U);
+      const uint32_t b_hi = (len == KB) ? blockIdx.x : sk_owner(first + KB - 1, G, U);
+      const bool owner = b_lo == blockIdx.x;
       float ch_scale = 1.0f, ch_bias = 0.0f;
-      if (n < p.N) {
+      if (owner && n < p.N) {
         if (FMT == FMT_W8)
           ch_scale = p.scale_is_f32 ? reinterpret_cast<const float*>(p.scales)[n]
                                     : __half2float(reinterpret_cast<const __half*>(p.scales)[n]);
         if (p.bias != nullptr) ch_bias = static_cast<float>(static_cast<const T*>(p.bias)[n]);
       }
-      const uint32_t slot = (seg_u == u0) ? 0u : 1u;
-      float* mine = p.partial + (static_cast<size_t>(blockIdx.x * 2u + slot) * p.tok) * kBlockN + ch;
+      const size_t per_slot = static_cast<size_t>(p.tok) * kBlockN;
+      uint32_t* mine = p.exchange + static_cast<size_t>(blockIdx.x) * per_slot + ch;
+      const bool collect = owner && b_hi > b_lo;   // only ever a block's last segment: the rings drain
+      // Up to sixteen token rows: the other blocks' partials are pulled into registers NOW,
+      // while this segment's MMAs are still running (the other blocks finished their part of
+      // the tile earlier), so that nothing but the addition is left once the accumulator is
+      // ready.  Every thread polls its own channel's words (bounded) and empties them.
+      const bool early = collect && rows <= 16;
+      float others[16];
+#pragma unroll
+      for (int m = 0; m < 16; ++m) others[m] = 0.0f;
+      if (early) {
+        for (uint32_t bb = b_lo + 1; bb <= b_hi; ++bb) {
+          uint32_t* src = p.exchange + static_cast<size_t>(bb) * per_slot + ch;
+          uint32_t v[16];
+          bool all = false;
+          for (uint32_t tries = 0; !all; ++tries) {
+            all = true;
+#pragma unroll
+            for (int m = 0; m < 16; ++m) {
+              v[m] = (m < rows) ? ld_relaxed_gpu_u32(src + m * kBlockN) : 0x80000000u;
+              all = all && v[m] != 0u;
+            }
+            if (!all) {
+              if (tries >= kSkExchangePolls || *abort_p) {
+                atomicOr(p.status, 16u);
+                break;
+              }
+              __nanosleep(300);
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < 16; ++m) {
+            others[m] += sk_decode(v[m]);                            // block order; absent rows add +0.0f
+            if (m < rows) __stcg(src + m * kBlockN, 0u);             // empty again for the next launch
+          }
+        }
+      }
       if (ok) {
         ok = wait_or_abort(acc_full, acc_phase, abort_p);
         if (!ok) flag_failure(abort_p, p.status, 8u);
       }
       acc_phase ^= 1u;
       tc_fence_after_sync();
-      // Read the accumulator out (sixteen columns at a time) and hand it back to the MMA warp
-      // at once; a whole tile goes to the output, a partial is parked in the workspace.
-      for (int c = 0; c < p.tok; c += 16) {
-        uint32_t r[16];
+      // Read the accumulator out eight columns (token rows) at a time and hand it back to the
+      // MMA warp as soon as the last of it is in registers.  A tile of this block alone goes
+      // to the output; a partial is parked in this block's exchange slot; an owner's own part
+      // goes to shared memory (the idle activation ring) to have the others' added to it.
+      const uint32_t sum_buf = x_ring + ch * 4;                    // [token row][128 channels] fp32
+      for (int c = 0; c < p.tok; c += 8) {
+        uint32_t r[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = 0u;
+        for (int j = 0; j < 8; ++j) r[j] = 0u;
         if (ok) {
-          tmem_ld_x16(acc_addr + c, r);
+          tmem_ld_x8(acc_addr + c, r);
           tmem_ld_wait();
         }
-        if (c + 16 >= p.tok) {
+        if (c + 8 >= p.tok) {
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty);
         }
-        if (whole) {
+        if (c >= rows) continue;
+        if (collect && !early) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c + j < rows) emit(c + j, n, __uint_as_float(r[j]) * ch_scale + ch_bias);
+          for (int j = 0; j < 8; ++j)
+            if (c + j < rows) st_shared_f32(sum_buf + (c + j) * 512, __uint_as_float(r[j]));
+        } else if (owner) {
+          // (c is 0 or 8 whenever `others` holds anything; otherwise it is all zeros)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float extra = c == 0 ? others[j] : (c == 8 ? others[8 + j] : 0.0f);
+            if (c + j < rows) emit(c + j, n, (__uint_as_float(r[j]) + extra) * ch_scale + ch_bias);
+          }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c + j < rows) mine[(c + j) * kBlockN] = __uint_as_float(r[j]);
+          for (int j = 0; j < 8; ++j)
+            if (c + j < rows) __stcg(mine + (c + j) * kBlockN, sk_encode(__uint_as_float(r[j])));
         }
       }
-      if (!whole) {
-        // count the partial; the last contributor of the tile sums them in block order
-        const uint32_t first = static_cast<uint32_t>(tile) * KB;
-        const uint32_t b_lo = sk_owner(first, G, U);
-        const uint32_t b_hi = sk_owner(first + KB - 1, G, U);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) {
-          const unsigned prev = atomicAdd(p.counters + tile, 1u);
-          *last_p = (prev == b_hi - b_lo) ? 1 : 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_p) {
-          __threadfence();
-          // Block b_lo parked this tile in slot 0 if its range begins exactly at the tile's
-          // first unit, in slot 1 if the tile begins inside its range; every later block has
-          // the tile under way at the start of its range: slot 0.
-          const uint32_t lo_slot = (sk_first_unit(b_lo, G, U) == first) ? 0u : 1u;
-          const size_t per_slot = static_cast<size_t>(p.tok) * kBlockN;
-          const float* base = p.partial + ch;
-          for (int t0 = 0; t0 < rows; t0 += 8) {
-            float acc[8];
+      if (collect && !early) {
+        // More than sixteen token rows.  The other blocks' partials, a batch at a time: one bulk copy per block brings its
+        // whole slot into the idle weight ring (every byte in flight at once: a look costs one
+        // trip to L2 whatever the row count), every thread checks its channel's words, and
+        // the look is repeated (bounded) until none reads as "not written".  Then they are
+        // added in block order and the slots are put back to zero.
+        const uint32_t slot_bytes = static_cast<uint32_t>(rows) * 512u;
+        const uint32_t stride = static_cast<uint32_t>(p.tok) * 512u;
+        const uint32_t room = static_cast<uint32_t>(S) * kWBytes / stride;
+        const uint32_t batch = room < 4u ? (room < 1u ? 1u : room) : 4u;
+        for (uint32_t bb = b_lo + 1; bb <= b_hi; bb += batch) {
+          const uint32_t nb = min(batch, b_hi - bb + 1);
+          bool all = false;
+          for (uint32_t tries = 0; !all; ++tries) {
+            if (threadIdx.x == 64) {
+              mbar_arrive_expect_tx(xg_full, nb * slot_bytes);
+              for (uint32_t z = 0; z < nb; ++z)
+                bulk_load(w_ring + z * stride, p.exchange + static_cast<size_t>(bb + z) * per_slot, slot_bytes, xg_full);
+            }
+            bool landed = wait_or_abort(xg_full, xg_phase, abort_p);
+            xg_phase ^= 1u;
+            bool mine_ok = landed;
+            for (uint32_t z = 0; z < nb && mine_ok; ++z)
+              for (int m = 0; m < rows; ++m)
+                mine_ok = mine_ok && __float_as_uint(ld_shared_f32(w_ring + z * stride + m * 512 + ch * 4)) != 0u;
+            all = epilogue_all(mine_ok);
+            if (!all) {
+              if (tries >= kSkExchangePolls || !landed || *abort_p) {
+                if (threadIdx.x == 64) atomicOr(p.status, 16u);
+                break;
+              }
+              __nanosleep(500);
+            }
+          }
+          for (uint32_t z = 0; z < nb; ++z) {
+            uint32_t* slot = p.exchange + static_cast<size_t>(bb + z) * per_slot + ch;
+            for (int m0 = 0; m0 < rows; m0 += 8) {
+              float a[8], b[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-            for (uint32_t bb = b_lo; bb <= b_hi; bb += 2) {
-              // two contributors per round: sixteen independent loads in flight
-              const bool two = bb + 1 <= b_hi;
-              const float* s0 = base + (static_cast<size_t>(bb) * 2u + (bb == b_lo ? lo_slot : 0u)) * per_slot +
-                                static_cast<size_t>(t0) * kBlockN;
-              const float* s1 = base + (static_cast<size_t>(bb + 1) * 2u) * per_slot + static_cast<size_t>(t0) * kBlockN;
-              float v0[8], v1[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                v0[e] = (t0 + e < rows) ? __ldcg(s0 + e * kBlockN) : 0.0f;
-                v1[e] = (two && t0 + e < rows) ? __ldcg(s1 + e * kBlockN) : 0.0f;
+              for (int j = 0; j < 8; ++j) {
+                const bool in = m0 + j < rows;
+                a[j] = in ? ld_shared_f32(sum_buf + (m0 + j) * 512) : 0.0f;
+                b[j] = in ? sk_decode(__float_as_uint(ld_shared_f32(w_ring + z * stride + (m0 + j) * 512 + ch * 4))) : 0.0f;
               }
 #pragma unroll
-              for (int e = 0; e < 8; ++e) acc[e] = (acc[e] + v0[e]) + v1[e];   // block order; + 0.0f is exact
+              for (int j = 0; j < 8; ++j) {
+                if (m0 + j < rows) {
+                  st_shared_f32(sum_buf + (m0 + j) * 512, a[j] + b[j]);
+                  __stcg(slot + (m0 + j) * kBlockN, 0u);             // empty again for the next launch
+                }
+              }
             }
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              if (t0 + e < rows) emit(t0 + e, n, acc[e] * ch_scale + ch_bias);
           }
-          if (et == 0) p.counters[tile] = 0u;      // ready for the next launch / graph replay
+          // every thread is done with the staged batch before the next one overwrites it
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        for (int m0 = 0; m0 < rows; m0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = (m0 + j < rows) ? ld_shared_f32(sum_buf + (m0 + j) * 512) : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (m0 + j < rows) emit(m0 + j, n, v[j] * ch_scale + ch_bias);
         }
       }
       left -= len;
-      seg_u += static_cast<uint32_t>(len);
       kb = 0;
       ++tile;
     }
@@ -635,8 +747,7 @@ static SkPlan sk_plan(int format, int M, int N, int K, int sms) {
 
 size_t sk_workspace_bytes(int format, int M, int N, int K) {
   if (!sk_geometry(format, M, N, K)) return 0;
-  const int tok = (M + 15) / 16 * 16;
-  return kWsPartialOffset + sizeof(float) * static_cast<size_t>(kSkMaxGrid) * 2 * tok * kBlockN;
+  return kWsExchangeOffset + kWsExchangeBytes;
 }
 
 bool sk_supported(const ForwardArgs& a) {
@@ -648,6 +759,17 @@ bool sk_supported(const ForwardArgs& a) {
     if (a.format == FMT_W4_ASYM && reinterpret_cast<uintptr_t>(a.zeros) % 16) return false;
   }
   return sk_geometry(a.format, a.M, a.N, a.K);
+}
+
+// Where the stream-K kernel measured faster than the tile kernel (B200, CUDA-graph replay over
+// rotating weights): 4-bit weights at up to sixteen token rows when a weight tile is shared by
+// few blocks (a block's share of units is at least half a tile's K), e.g. 4096 -> 12288 at
+// M = 1 / 16: 12.3 / 14.2 us against 14.1 / 15.0.  It lost on int8 (4096 -> 12288 M = 16: 18.3
+// against 16.9 us), on deep K (12288 -> 4096 M = 16: 17.2 against 16.0) and above sixteen rows.
+bool sk_preferred(int format, int M, int N, int K) {
+  if (format == FMT_W8 || M > 16 || !sk_geometry(format, M, N, K)) return false;
+  const SkPlan pl = sk_plan(format, M, N, K, sm_count());
+  return 2u * (pl.units / static_cast<uint32_t>(pl.grid)) >= static_cast<uint32_t>(pl.kb_total);
 }
 
 int sk_gather_arrivals(int, int, int, int) { return 0; }
@@ -732,8 +854,7 @@ static int launch_sk_typed(const ForwardArgs& a, const SkPlan& pl) {
   p.swiglu = a.swiglu ? 1 : 0;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   p.status = reinterpret_cast<unsigned*>(ws);
-  p.counters = reinterpret_cast<unsigned*>(ws + kWsCountersOffset);
-  p.partial = reinterpret_cast<float*>(ws + kWsPartialOffset);
+  p.exchange = reinterpret_cast<uint32_t*>(ws + kWsExchangeOffset);
 
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(pl.grid);
@@ -760,8 +881,7 @@ static int launch_sk_typed(const ForwardArgs& a, const SkPlan& pl) {
 
 int launch_forward_sk(const ForwardArgs& a) {
   const SkPlan pl = sk_plan(a.format, a.M, a.N, a.K, sm_count());
-  const size_t need = kWsPartialOffset + sizeof(float) * static_cast<size_t>(pl.grid) * 2 * pl.tok * kBlockN;
-  if (a.workspace == nullptr || a.workspace_bytes < need) return B200Q_ERR_WORKSPACE;
+  if (a.workspace == nullptr || a.workspace_bytes < kWsExchangeOffset + kWsExchangeBytes) return B200Q_ERR_WORKSPACE;
   const bool h = a.act_dtype == B200Q_F16;
   switch (a.format) {
     case FMT_W8:

@@ -1113,12 +1113,13 @@ static TcPlan make_plan(int format, int M, int N, int K, bool no_split = false) 
 }
 
 // Workspace a forward of this geometry may need, whichever kernel serves it: the fixed
-// header (status, counters, argmax keys) plus the larger of the two kernels' fp32 partials.
+// header (status, counters, argmax keys), the stream-K exchange region for token counts that
+// kernel takes, or the tile kernel's split-K partials behind it.
 size_t tc_workspace_bytes(int format, int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   TcPlan pl = make_plan(format, M, N, K);
-  size_t bytes = kWsPartialOffset;
-  if (pl.splits > 1) bytes += sizeof(float) * static_cast<size_t>(pl.splits) * M * N;
+  size_t bytes = kWsExchangeOffset;
+  if (pl.splits > 1) bytes = kWsPartialOffset + sizeof(float) * static_cast<size_t>(pl.splits) * M * N;
   const size_t sk = sk_workspace_bytes(format, M, N, K);
   return sk > bytes ? sk : bytes;
 }
@@ -1326,7 +1327,7 @@ void tc_describe_plan(int format, int M, int N, int K, char* text, size_t size) 
     std::snprintf(text, size, "nothing to launch");
     return;
   }
-  if (sk_describe(format, M, N, K, text, size)) return;
+  if (sk_preferred(format, M, N, K) && sk_describe(format, M, N, K, text, size)) return;
   const TcPlan pl = make_plan(format, M, N, K);
   std::snprintf(text, size, "wq_gemm_tc_kernel<%s,dw%d> tok=%d tiles=%dx%d splits=%d smem=%zu tmem=%d",
                 format == FMT_W8 ? "w8" : (format == FMT_W4_REF ? "w4_ref" : "w4_asym"), pl.dw, pl.tok,
@@ -1358,12 +1359,13 @@ int launch_forward_tc(const ForwardArgs& a) {
   if (!tc_supported(a)) return B200Q_ERR_UNSUPPORTED;
   if (a.workspace == nullptr) return B200Q_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(a.workspace) % 256) return B200Q_ERR_ALIGNMENT;
-  if (sk_supported(a)) return launch_forward_sk(a);
+  if (a.force_streamk && !sk_supported(a)) return B200Q_ERR_UNSUPPORTED;
+  if (sk_supported(a) && (a.force_streamk || sk_preferred(a.format, a.M, a.N, a.K))) return launch_forward_sk(a);
   // The fused argmax never splits K: it needs the header (counters and row keys) only.
   if (a.argmax && a.M > kMaxArgmaxRows) return B200Q_ERR_UNSUPPORTED;
   const TcPlan pl = make_plan(a.format, a.M, a.N, a.K, a.argmax);
-  size_t need = kWsPartialOffset;
-  if (pl.splits > 1) need += sizeof(float) * static_cast<size_t>(pl.splits) * a.M * a.N;
+  size_t need = kWsExchangeOffset;
+  if (pl.splits > 1) need = kWsPartialOffset + sizeof(float) * static_cast<size_t>(pl.splits) * a.M * a.N;
   if (a.workspace_bytes < need) return B200Q_ERR_WORKSPACE;
   const bool h = a.act_dtype == B200Q_F16;
   switch (a.format) {

@@ -34,6 +34,7 @@ struct ForwardArgs {
   bool static_weights;  // weights/scales/zeros/bias were written long before this call
   bool swiglu;          // rows are interleaved (gate, up) pairs; y has N/2 columns of silu(gate) * up
   bool argmax;          // y is u64 keys[M], zeroed by the caller: row-wise maximum and its channel
+  bool force_streamk;   // B200Q_KERNEL_STREAMK: the persistent stream-K variant or nothing
   const b200q_gather* gather;  // fused all-gather destinations, or null
   cudaStream_t stream;
 };

@@ -21,17 +21,22 @@ namespace b200q {
 constexpr int kBlockN = 128;                 // output channels per tile (UMMA M)
 constexpr int kBlockK = 128;                 // K elements per pipeline step
 
-// Workspace layout (fixed, so that calls of different geometry never see one another's
-// leftovers as counters or keys):
-//   [0, 256)            status word
-//   [256, 64 KiB)       split-K / stream-K tile counters, zero between launches
-//   [64 KiB, 128 KiB)   row keys of the fused argmax (8 bytes per row), zero between launches
-//   [128 KiB, ...)      fp32 partials (never read before they are written: no zeroing needed)
+// Workspace layout (fixed, so that calls of different geometry or kernel never see one
+// another's leftovers as counters, keys or partials):
+//   [0, 256)                 status word
+//   [256, 64 KiB)            split-K tile counters of the tile kernel, zero between launches
+//   [64 KiB, 128 KiB)        row keys of the fused argmax (8 bytes per row), zero between launches
+//   [128 KiB, 128 KiB+5 MiB) partial exchange of the stream-K kernel (one slot per block,
+//                            64 rows x 128 channels x 4 bytes), all zero between launches
+//   [128 KiB + 5 MiB, ...)   fp32 split-K partials of the tile kernel (always written before
+//                            they are read: no zeroing needed)
 constexpr size_t kWsCountersOffset = 256;
 constexpr size_t kWsKeysOffset = 64 * 1024;
-constexpr size_t kWsPartialOffset = 128 * 1024;
+constexpr size_t kWsExchangeOffset = 128 * 1024;
+constexpr size_t kWsExchangeBytes = 5 * 1024 * 1024;
+constexpr size_t kWsPartialOffset = kWsExchangeOffset + kWsExchangeBytes;
 constexpr int kMaxSplitTiles = static_cast<int>((kWsKeysOffset - kWsCountersOffset) / sizeof(unsigned));
-constexpr int kMaxArgmaxRows = static_cast<int>((kWsPartialOffset - kWsKeysOffset) / sizeof(unsigned long long));
+constexpr int kMaxArgmaxRows = static_cast<int>((kWsExchangeOffset - kWsKeysOffset) / sizeof(unsigned long long));
 
 template <int FMT>
 struct PackedStage {
@@ -201,6 +206,7 @@ bool debug_plan_enabled();
 
 // gemm_sk.cu: persistent stream-K kernel for token tiles of at most 64 rows.
 bool sk_supported(const ForwardArgs& a);
+bool sk_preferred(int format, int M, int N, int K);
 size_t sk_workspace_bytes(int format, int M, int N, int K);
 int sk_gather_arrivals(int format, int M, int N, int K);
 int launch_forward_sk(const ForwardArgs& a);

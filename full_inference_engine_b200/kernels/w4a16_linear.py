@@ -15,7 +15,8 @@ from .w4a16_format import (  # noqa: F401  (re-exported like the reference modul
     GEMV_MAX_ROWS, GROUP_SIZE, OFFSET, quantize_weight_w4_grouped,
 )
 
-_KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERNEL_TC}
+_KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERNEL_TC,
+            "streamk": _lib.KERNEL_STREAMK}
 
 
 def _forward(inputs, packed, scales, zeros, bias, group_size, kernel, where, static_weights=False,
@@ -84,7 +85,7 @@ def w4a16_linear(inputs: torch.Tensor, packed: torch.Tensor, scales: torch.Tenso
     if inputs.ndim != 2 or packed.ndim != 2 or packed.dtype is not want:
         raise ValueError("inputs must be 2D fp16 and packed weights 2D uint8")
     if kernel not in _KERNELS:
-        raise ValueError(f"kernel must be auto, gemv or dot; got {kernel!r}")
+        raise ValueError(f"kernel must be auto, gemv, dot or streamk; got {kernel!r}")
     m, k = inputs.shape
     n, packed_k = packed.shape
     if group_size % 32 or group_size < 32:

@@ -6,7 +6,8 @@ import torch
 
 from .. import _lib
 
-_KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERNEL_TC}
+_KERNELS = {"auto": _lib.KERNEL_AUTO, "gemv": _lib.KERNEL_SIMT, "dot": _lib.KERNEL_TC,
+            "streamk": _lib.KERNEL_STREAMK}
 
 
 def _quantize(weight: torch.Tensor, mode: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -62,7 +63,7 @@ def w8a16_linear(inputs: torch.Tensor, qweight: torch.Tensor, scales: torch.Tens
     if k % 32:
         raise ValueError("W8A16 kernel requires input width divisible by 32")
     if kernel not in _KERNELS:
-        raise ValueError(f"kernel must be auto, gemv or dot; got {kernel!r}")
+        raise ValueError(f"kernel must be auto, gemv, dot or streamk; got {kernel!r}")
     if inputs.dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("inputs must be fp16 or bf16")
     if swiglu_pairs and n % 2:

@@ -60,7 +60,13 @@ typedef enum b200q_w4_layout {
 typedef enum b200q_kernel {
   B200Q_KERNEL_AUTO = 0,  /* pick by M                                         */
   B200Q_KERNEL_SIMT = 1,  /* CUDA-core split-K GEMV (decode rows)              */
-  B200Q_KERNEL_TC = 2     /* tcgen05 tensor-core GEMM, weights on the M side   */
+  B200Q_KERNEL_TC = 2,    /* tcgen05 tensor-core GEMM, weights on the M side:
+                             AUTO's choice between its two variants             */
+  B200Q_KERNEL_STREAMK = 3 /* the persistent stream-K variant of the tensor-core
+                             kernel (M <= 64, K a multiple of 1024 for INT4);
+                             B200Q_ERR_UNSUPPORTED for other geometries.  AUTO
+                             takes it where it measured faster: INT4, M <= 16,
+                             weight tiles shared by few blocks                  */
 } b200q_kernel;
 
 /* OR-ed into the `kernel` argument of a forward call.
@@ -154,10 +160,12 @@ int b200q_w4_dequant(const void* packed, const void* scales, const void* zeros,
  * Bytes of workspace a forward call of this geometry may use (0 = none).
  * `format`: 8 for W8A16, 4 for either INT4 layout.  Layout: [0, 256) a status
  * word, [256, 64 KiB) tile counters, [64 KiB, 128 KiB) the row keys of the fused
- * argmax, then fp32 partial sums.  The workspace must be zero-filled once when it
- * is allocated; every call leaves status, counters and keys at zero again, and the
- * partials are always written before they are read, so graph replays need no
- * memset and calls of any kind may follow one another on the same workspace.
+ * argmax, [128 KiB, 128 KiB + 5 MiB) the partial exchange of the decode kernel,
+ * then fp32 split-K partial sums.  The workspace must be zero-filled once when it
+ * is allocated; every call leaves status, counters, keys and the exchange region
+ * at zero again, and the split-K partials are always written before they are
+ * read, so graph replays need no memset and calls of any kind may follow one
+ * another on the same workspace.
  * Calls that may overlap on the GPU (different streams) need a workspace each:
  * counters, partials and keys of two running kernels must not share memory.
  * A call with B200Q_FLAG_ARGMAX needs only the first 128 KiB.

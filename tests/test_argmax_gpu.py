@@ -93,11 +93,11 @@ def test_module_argmax_matches_forward_argmax():
     assert head.argmax(x).shape == (2, 5)
 
 
-def _partials_region(ws: torch.Tensor) -> torch.Tensor:
-    return ws[128 * 1024:]
+EXCHANGE = slice(128 * 1024, 128 * 1024 + 5 * 1024 * 1024)     # the decode kernel's partial exchange
+PARTIALS = slice(128 * 1024 + 5 * 1024 * 1024, None)           # the tile kernel's split-K partials
 
 
-@pytest.mark.parametrize("m,k,n", [(16, 12288, 4096), (144, 12288, 1024)])
+@pytest.mark.parametrize("m,k,n", [(16, 4096, 12288), (16, 12288, 4096), (144, 12288, 1024)])
 def test_argmax_after_a_forward_that_left_partials_in_the_shared_workspace(m, k, n):
     """A decode step runs projections whose K is split (fp32 partials stay behind in the
     workspace) and then the head's argmax on the SAME workspace: the keys have a region of
@@ -109,7 +109,10 @@ def test_argmax_after_a_forward_that_left_partials_in_the_shared_workspace(m, k,
     w4a16_linear.w4a16_linear(x, packed, scales)
     ws = _lib.workspace_for(device, 256)
     torch.cuda.synchronize()
-    assert bool((_partials_region(ws) != 0).any()), "the split path did not go through the workspace"
+    assert not bool(ws[EXCHANGE].any()), "the exchange region was not left empty"
+    if "wq_gemm_sk_kernel" not in _lib.describe_plan(4, m, n, k):
+        # the tile kernel's K split is too deep for a cluster here: fp32 partials stay behind
+        assert bool(ws[PARTIALS].any()), "the split path did not go through the workspace"
     head_k, vocab = 1024, 5000
     hp, hs = w4.quantize_weight_w4_grouped(torch.randn(vocab, head_k, device=DEV) * 0.05)
     hx = torch.randn(m, head_k, device=DEV).half()

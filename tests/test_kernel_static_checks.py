@@ -56,8 +56,9 @@ def test_no_multicast_loads_traps_or_device_asserts(path):
     code = _code(path)
     assert "multicast::cluster" not in code or "tcgen05.commit" in code.split("multicast::cluster")[0][-200:], \
         f"{path.name}: a cluster-multicast copy"
-    for banned in ("__trap", "assert(", "multimem", "wgmma", "nanosleep(0x7fffffff"):
+    for banned in ("__trap", "multimem", "wgmma", "nanosleep(0x7fffffff"):
         assert banned not in code, f"{path.name} contains {banned}"
+    assert not re.search(r"(?<!static_)\bassert\(", code), f"{path.name} has a device-side assert"
 
 
 @pytest.mark.parametrize("path", SOURCES, ids=lambda p: p.name)
@@ -135,12 +136,14 @@ def test_header_symbols_match_the_binding_table():
 def test_workspace_layout_constants_are_consistent():
     common = _code(CSRC / "tc_common.cuh")
     keys = int(re.search(r"kWsKeysOffset\s*=\s*(\d+)\s*\*\s*1024", common).group(1)) * 1024
-    partial = int(re.search(r"kWsPartialOffset\s*=\s*(\d+)\s*\*\s*1024", common).group(1)) * 1024
-    assert 256 < keys < partial
-    # counters, keys and partials never share an address: the layout the header documents
+    exchange = int(re.search(r"kWsExchangeOffset\s*=\s*(\d+)\s*\*\s*1024", common).group(1)) * 1024
+    exchange_mib = int(re.search(r"kWsExchangeBytes\s*=\s*(\d+)\s*\*\s*1024\s*\*\s*1024", common).group(1))
+    assert 256 < keys < exchange
+    assert re.search(r"kWsPartialOffset\s*=\s*kWsExchangeOffset\s*\+\s*kWsExchangeBytes", common)
+    # counters, keys, exchange words and partials never share an address: the layout the header documents
     header = HEADER.read_text()
-    assert f"[256, {keys // 1024} KiB)" in header and f"[{keys // 1024} KiB, {partial // 1024} KiB)" in header
-    for name in ("gemm_tc.cu", "gemm_sk.cu"):
-        code = _code(CSRC / name)
-        assert "ws + kWsPartialOffset" in code and "ws + kWsCountersOffset" in code
-    assert "ws + kWsKeysOffset" in _code(CSRC / "gemm_tc.cu")
+    assert f"[256, {keys // 1024} KiB)" in header and f"[{keys // 1024} KiB, {exchange // 1024} KiB)" in header
+    assert f"[{exchange // 1024} KiB, {exchange // 1024} KiB + {exchange_mib} MiB)" in header
+    tile, stream = _code(CSRC / "gemm_tc.cu"), _code(CSRC / "gemm_sk.cu")
+    assert "ws + kWsPartialOffset" in tile and "ws + kWsCountersOffset" in tile and "ws + kWsKeysOffset" in tile
+    assert "ws + kWsExchangeOffset" in stream and "kWsPartialOffset" not in stream

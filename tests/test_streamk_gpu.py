@@ -42,8 +42,8 @@ def _quantized(fmt, weight):
 
 def _forward(fmt, x, qw, bias=None, **kw):
     if fmt == "w8":
-        return w8a16_linear.w8a16_linear(x, qw[0], qw[1], bias, kernel="dot", **kw)
-    return w4a16_linear.w4a16_linear(x, qw[0], qw[1], bias, zeros=qw[2], kernel="dot", **kw)
+        return w8a16_linear.w8a16_linear(x, qw[0], qw[1], bias, kernel="streamk", **kw)
+    return w4a16_linear.w4a16_linear(x, qw[0], qw[1], bias, zeros=qw[2], kernel="streamk", **kw)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -72,7 +72,7 @@ def test_streamk_shape_sweep(fmt):
     three groups and one long K; one quantised matrix per (N, K), sliced inputs per M."""
     rng = np.random.default_rng(7)
     worst = 0.0
-    for k in (128, 256, 384, 5120):
+    for k in (1024, 2048, 5120) if fmt != "w8" else (128, 256, 384, 5120):
         for n in (1, 8, 127, 128, 129, 200, 257, 1000):
             torch.manual_seed(n * 7 + k)
             qw, deq = _quantized(fmt, torch.randn(n, k, device=DEV) * 0.05)

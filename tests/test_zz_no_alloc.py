@@ -37,9 +37,12 @@ def _call(fn, x, packed, scales, y, m, n, k, *workspace, flags=0):
 def test_static_scratch_entry_point_matches_the_workspace_entry_point(m):
     lib = _lib.library()
     torch.manual_seed(m)
-    # M <= 64: the stream-K kernel, whose blocks share tiles (12 tiles over far more blocks);
-    # M = 144: the tile kernel with a K split too deep for a cluster.  Both park fp32 partials.
-    k, n = (12288, 1536) if m <= 64 else (12288, 1024)
+    # M <= 16: a shape the stream-K kernel takes (75 weight tiles shared among the blocks, partials
+    # exchanged through the scratch); M = 64 / 144: the tile kernel with a K split too deep for a
+    # cluster (fp32 partials parked in the scratch).
+    k, n = (1024, 9600) if m <= 16 else (12288, 1024)
+    plan = _lib.describe_plan(4, m, n, k)
+    assert ("wq_gemm_sk_kernel" in plan) == (m <= 16), plan
     packed, scales = w4.quantize_weight_w4_grouped((torch.randn(n, k, device="cuda") * 0.02))
     deq = oracle.unpack_w4(packed.cpu().numpy(), scales.cpu().numpy(), k)
     need = _lib.workspace_bytes(4, m, n, k)
@@ -62,8 +65,12 @@ def test_static_scratch_entry_point_matches_the_workspace_entry_point(m):
         truth = oracle.linear_fp32(x.float().cpu().numpy(), deq)
         ok, ratio = oracle.within_tolerance(actual.float().cpu().numpy(), truth)
         assert ok, f"call {call}: {ratio} of max|ref| against the oracle"
-        # the workspace entry point parked partials in the caller's buffer: the geometry needs them
-        assert bool((workspace[128 * 1024:] != 0).any()), "this geometry was expected to park partials"
+        # this geometry exchanges partial sums through the scratch: the tile kernel (M > 64) leaves
+        # its fp32 partials behind, the decode kernel hands every exchange word back as zero
+        if m > 16:
+            assert bool(workspace[128 * 1024 + 5 * 1024 * 1024:].any()), "expected split-K partials"
+        else:
+            assert not bool(workspace[128 * 1024:].any()), "the exchange region was not left empty"
     # the head's fused argmax on the same array, after calls that left partials in it
     vocab, head_k = 3000, 1024
     hp, hs = w4.quantize_weight_w4_grouped(torch.randn(vocab, head_k, device="cuda") * 0.05)
