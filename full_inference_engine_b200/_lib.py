@@ -77,6 +77,27 @@ _SIGNATURES.update({
     "b200q_gather_wait": (_c_int, [_gather_p, _c_int, _c_void_p]),
 })
 
+
+
+class Reduce(ctypes.Structure):
+    """``b200q_reduce`` of include/b200q.h: peer-mapped output, signal and inbox pointers."""
+
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("y_peer", ctypes.c_void_p * 8),
+                ("signal_peer", ctypes.c_void_p * 8), ("inbox_peer", ctypes.c_void_p * 8)]
+
+
+_reduce_p = ctypes.POINTER(Reduce)
+_SIGNATURES.update({
+    "b200q_reduce_tiles": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
+    "b200q_w4a16_forward_reduce": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_int, _c_void_p,
+                                            _c_void_p, _c_int, _c_void_p, _reduce_p, _c_i64, _c_int, _c_int,
+                                            _c_int, _c_void_p, _c_size, _c_int, _c_void_p]),
+    "b200q_w8a16_forward_reduce": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_void_p, _c_int,
+                                            _c_void_p, _reduce_p, _c_i64, _c_int, _c_int, _c_int,
+                                            _c_void_p, _c_size, _c_int, _c_void_p]),
+    "b200q_reduce_wait": (_c_int, [_reduce_p, _c_int, _c_void_p]),
+})
+
 _lib = None
 _lock = threading.Lock()
 

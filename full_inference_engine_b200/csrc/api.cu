@@ -287,6 +287,92 @@ int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   return launch_forward_tc(a);
 }
 
+static int check_reduce(const b200q_reduce* r, int64_t ldy, int n) {
+  if (!r || r->world < 1 || r->world > 8 || r->rank < 0 || r->rank >= r->world) return B200Q_ERR_INVALID;
+  if (ldy < n || n % r->world || (n / r->world) % 128) return B200Q_ERR_INVALID;
+  for (int i = 0; i < r->world; ++i) {
+    if (!r->y_peer[i] || !r->signal_peer[i] || !r->inbox_peer[i]) return B200Q_ERR_INVALID;
+    if (reinterpret_cast<uintptr_t>(r->signal_peer[i]) % 8 || reinterpret_cast<uintptr_t>(r->inbox_peer[i]) % 4)
+      return B200Q_ERR_ALIGNMENT;
+  }
+  return B200Q_OK;
+}
+
+int b200q_reduce_tiles(int format, int M, int N, int K_local, int group, int world) {
+  if (format == 8) return (K_local % 64 == 0) ? tc_reduce_tiles(FMT_W8, M, N, K_local, world) : 0;
+  if (format == 4) return (group == 128 && K_local % 128 == 0) ? tc_reduce_tiles(FMT_W4_REF, M, N, K_local, world) : 0;
+  return 0;
+}
+
+int b200q_w4a16_forward_reduce(const void* x, int64_t ldx, int act_dtype, const void* packed,
+                               int64_t ldw, int layout, const void* scales, const void* zeros,
+                               int group, const void* bias, const b200q_reduce* reduce, int64_t ldy,
+                               int M, int N, int K_local, void* workspace, size_t workspace_bytes,
+                               int flags, void* stream) {
+  if (M < 0 || N < 0 || K_local <= 0) return B200Q_ERR_INVALID;
+  if (M == 0 || N == 0) return B200Q_OK;
+  if (!x || !packed || !scales) return B200Q_ERR_INVALID;
+  if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (layout == B200Q_W4_ASYM_ZP_INT32) {
+    if (!zeros) return B200Q_ERR_INVALID;
+  } else if (layout != B200Q_W4_REF_SPLIT_HALF_SYM) {
+    return B200Q_ERR_INVALID;
+  }
+  if (group <= 0 || K_local % group) return B200Q_ERR_INVALID;
+  if (ldx < K_local || ldw < K_local / 2) return B200Q_ERR_INVALID;
+  if (flags & (B200Q_FLAG_SWIGLU_PAIRS | B200Q_FLAG_ARGMAX)) return B200Q_ERR_INVALID;
+  if (int st = check_reduce(reduce, ldy, N)) return st;
+  if (b200q_reduce_tiles(4, M, N, K_local, group, reduce->world) == 0) return B200Q_ERR_UNSUPPORTED;
+  ForwardArgs a{};
+  a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
+  a.w = packed; a.ldw = ldw;
+  a.format = layout == B200Q_W4_ASYM_ZP_INT32 ? FMT_W4_ASYM : FMT_W4_REF;
+  a.scales = scales; a.scale_dtype = B200Q_F16; a.zeros = zeros; a.group = group;
+  a.bias = bias; a.y = reduce->y_peer[reduce->rank]; a.ldy = ldy; a.M = M; a.N = N; a.K = K_local;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.reduce = reduce;
+  a.static_weights = (flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_forward_tc(a);
+}
+
+int b200q_w8a16_forward_reduce(const void* x, int64_t ldx, int act_dtype, const int8_t* qweight,
+                               int64_t ldw, const void* scales, int scale_dtype, const void* bias,
+                               const b200q_reduce* reduce, int64_t ldy, int M, int N, int K_local,
+                               void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  if (M < 0 || N < 0 || K_local <= 0) return B200Q_ERR_INVALID;
+  if (M == 0 || N == 0) return B200Q_OK;
+  if (!x || !qweight || !scales) return B200Q_ERR_INVALID;
+  if (act_dtype != B200Q_F16 && act_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (scale_dtype != B200Q_F16 && scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
+  if (ldx < K_local || ldw < K_local) return B200Q_ERR_INVALID;
+  if (flags & (B200Q_FLAG_SWIGLU_PAIRS | B200Q_FLAG_ARGMAX)) return B200Q_ERR_INVALID;
+  if (int st = check_reduce(reduce, ldy, N)) return st;
+  if (b200q_reduce_tiles(8, M, N, K_local, 0, reduce->world) == 0) return B200Q_ERR_UNSUPPORTED;
+  ForwardArgs a{};
+  a.x = x; a.ldx = ldx; a.act_dtype = act_dtype;
+  a.w = qweight; a.ldw = ldw; a.format = FMT_W8;
+  a.scales = scales; a.scale_dtype = scale_dtype; a.zeros = nullptr; a.group = 0;
+  a.bias = bias; a.y = reduce->y_peer[reduce->rank]; a.ldy = ldy; a.M = M; a.N = N; a.K = K_local;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.reduce = reduce;
+  a.static_weights = (flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_forward_tc(a);
+}
+
+int b200q_reduce_wait(const b200q_reduce* reduce, int tiles_per_rank, void* stream) {
+  if (!reduce || reduce->world < 1 || reduce->world > 8 || tiles_per_rank <= 0) return B200Q_ERR_INVALID;
+  if (reduce->rank < 0 || reduce->rank >= reduce->world || !reduce->signal_peer[reduce->rank])
+    return B200Q_ERR_INVALID;
+  b200q_gather g{};
+  g.rank = reduce->rank;
+  g.world = reduce->world;
+  for (int i = 0; i < 8; ++i) g.signal_peer[i] = reduce->signal_peer[i];
+  return launch_gather_wait(&g, static_cast<unsigned long long>(tiles_per_rank) * reduce->world,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int b200q_gather_wait(const b200q_gather* gather, int tiles_per_rank, void* stream) {
   if (!gather || gather->world < 1 || gather->world > 8 || tiles_per_rank <= 0) return B200Q_ERR_INVALID;
   if (gather->rank < 0 || gather->rank >= gather->world || !gather->signal_peer[gather->rank])

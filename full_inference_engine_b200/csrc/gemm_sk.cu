@@ -753,6 +753,7 @@ size_t sk_workspace_bytes(int format, int M, int N, int K) {
 bool sk_supported(const ForwardArgs& a) {
   if (a.argmax) return false;
   if (a.gather != nullptr && a.gather->world > 1) return false;
+  if (a.reduce != nullptr && a.reduce->world > 1) return false;
   if (a.format != FMT_W8) {
     if (a.group != 128) return false;
     if (reinterpret_cast<uintptr_t>(a.scales) % 16) return false;

@@ -72,6 +72,13 @@ struct TcParams {
   int g_world, g_rank, g_col0;
   void* g_y[8];
   unsigned long long* g_sig[8];   // each rank's signal block (see GatherSignal)
+  // fused all-reduce of a row-parallel (K-sharded) forward (reduce != 0, g_world > 1): every
+  // rank computes a partial [M, N]; the rank that owns a column block adds the other ranks'
+  // partials (delivered into its inbox as self-validating fp32 words) in rank order and
+  // stores the finished tile into every rank's y
+  int reduce;
+  int r_cols;                     // output columns owned by each rank (a multiple of 128)
+  uint32_t* r_inbox[8];           // each rank's inbox: [world][M][r_cols] words, all zero between calls
   unsigned* counters;  // [m_tiles * n_tiles], zero between launches
   unsigned* status;    // device status word (non-zero: a bounded wait expired)
 };
@@ -466,7 +473,7 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int m_base = m_tile * p.tok;
     const uint32_t tmem_row = tmem_base + (static_cast<uint32_t>(lane_quarter * 32) << 16);
     // destinations: this rank's y, or with the fused all-gather the same tile in every rank's y
-    const bool gather = p.g_world > 1;
+    const bool gather = p.g_world > 1 && !p.reduce;
     const int ndst = gather ? p.g_world : 1;
     const int col0 = gather ? p.g_col0 : 0;
     T* ydst[8];
@@ -500,7 +507,79 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                                   : __half2float(reinterpret_cast<const __half*>(p.scales)[n]);
       if (p.bias != nullptr) ch_bias = static_cast<float>(static_cast<const T*>(p.bias)[n]);
     }
-    if (p.argmax) {
+    if (p.reduce) {
+      // Row-parallel forward: this block holds the partial of its tile over this rank's K
+      // shard.  The tile's columns belong to one owner rank.  Every other rank sends its partial
+      // to the owner's inbox through peer memory as self-validating words (an fp32 value v
+      // travels as bits(v + 0.0f) ^ 0x80000000, never 0; 0 means "not written"), so the owner
+      // needs no flag: it polls the words themselves (bounded), adds the partials in rank
+      // order — a fixed order, identical on every run — adds the bias, rounds once, and stores
+      // the finished tile into the output of every rank; then it counts the tile on every rank
+      // exactly as the fused all-gather does.
+      const int owner = (n_tile * kBlockN) / p.r_cols;
+      const int n_local = n - owner * p.r_cols;
+      if (owner == p.g_rank) gather_wait_ready();          // peers have consumed the previous output
+      for (int c = 0; c < half_cols; c += 8) {
+        uint32_t r[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        if (acc_ok && nkb > 0) {
+          tmem_ld_x8(tmem_row + (c_begin + c), r);
+          tmem_ld_wait();
+        }
+        const int m0 = m_base + c_begin + c;
+        if (owner != p.g_rank) {
+          uint32_t* dst = p.r_inbox[owner] + (static_cast<size_t>(p.g_rank) * p.M + m0) * p.r_cols + n_local;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (m0 + j < p.M && n < p.N)
+              dst[static_cast<size_t>(j) * p.r_cols] = __float_as_uint(__uint_as_float(r[j]) + 0.0f) ^ 0x80000000u;
+          continue;
+        }
+        float sum[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
+        for (int src = 0; src < p.g_world; ++src) {
+          if (src == p.g_rank) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(r[j]);
+            continue;
+          }
+          uint32_t* from = p.r_inbox[p.g_rank] + (static_cast<size_t>(src) * p.M + m0) * p.r_cols + n_local;
+          uint32_t v[8];
+          bool all = false;
+          for (uint32_t tries = 0; !all; ++tries) {
+            all = true;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[j] = 0x80000000u;
+              if (m0 + j < p.M && n < p.N)
+                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v[j]) : "l"(from + static_cast<size_t>(j) * p.r_cols) : "memory");
+              all = all && v[j] != 0u;
+            }
+            if (!all) {
+              if (tries >= (1u << 22) || *abort_p) {      // about five seconds, like the gather waits
+                p.g_sig[p.g_rank][kSigStatus] = 4ull;
+                break;
+              }
+              __nanosleep(tries < 4096 ? 40 : 1000);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            sum[j] += __uint_as_float(v[j] ^ 0x80000000u);
+            if (m0 + j < p.M && n < p.N) from[static_cast<size_t>(j) * p.r_cols] = 0u;   // empty for the next call
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (m0 + j < p.M && n < p.N) {
+            const T out = from_float<T>(sum[j] * ch_scale + ch_bias);
+            for (int d = 0; d < p.g_world; ++d)
+              static_cast<T*>(p.g_y[d])[static_cast<int64_t>(m0 + j) * p.ldy + n] = out;
+          }
+        }
+      }
+      if (owner == p.g_rank) gather_signal_done();     // (a tile has one owner: uniform per block)
+    } else if (p.argmax) {
       // Row-wise argmax instead of the outputs (greedy decoding over an output head): every
       // value is rounded to the activation dtype exactly as the plain path would store it,
       // mapped to an order-preserving 16-bit code, and reduced warp -> block (shared-memory
@@ -1180,10 +1259,11 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
   // all-gather (peer pointers, one copy per rank) and split-K keep their own store paths.
   CUtensorMap tm_y{};
   const bool gathering = a.gather != nullptr && a.gather->world > 1;
+  const bool reducing = a.reduce != nullptr && a.reduce->world > 1;
   const int n_out = a.swiglu ? a.N / 2 : a.N;
   // (The TMA engine clips the innermost dimension in 16-byte units: measured, a 500-column fp16
   // output had columns 500..503 written.  So the row width must be whole 16-byte units too.)
-  const bool y_tma = !gathering && !a.argmax && pl.splits == 1 && (a.ldy % 8 == 0) && (n_out % 8 == 0) &&
+  const bool y_tma = !gathering && !reducing && !a.argmax && pl.splits == 1 && (a.ldy % 8 == 0) && (n_out % 8 == 0) &&
                      (reinterpret_cast<uintptr_t>(a.y) % 16 == 0);
   if (y_tma) {
     const CUtensorMapDataType ydt = (a.act_dtype == B200Q_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -1231,6 +1311,20 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
     for (int d = 0; d < 8; ++d) {
       p.g_y[d] = d < a.gather->world ? a.gather->y_peer[d] : nullptr;
       p.g_sig[d] = d < a.gather->world ? static_cast<unsigned long long*>(a.gather->signal_peer[d]) : nullptr;
+    }
+  }
+  p.reduce = 0;
+  if (reducing) {
+    p.reduce = 1;
+    p.g_world = a.reduce->world;
+    p.g_rank = a.reduce->rank;
+    p.g_col0 = 0;
+    p.r_cols = a.N / a.reduce->world;
+    for (int d = 0; d < 8; ++d) {
+      const bool in = d < a.reduce->world;
+      p.g_y[d] = in ? a.reduce->y_peer[d] : nullptr;
+      p.g_sig[d] = in ? static_cast<unsigned long long*>(a.reduce->signal_peer[d]) : nullptr;
+      p.r_inbox[d] = in ? static_cast<uint32_t*>(a.reduce->inbox_peer[d]) : nullptr;
     }
   }
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
@@ -1311,6 +1405,14 @@ static int launch_tc_width(const ForwardArgs& a, const TcPlan& pl) {
   return pl.dw == 16 ? launch_tc_typed<FMT, T, 16>(a, pl) : launch_tc_typed<FMT, T, 8>(a, pl);
 }
 
+// Tiles one rank owns (finishes and announces on every rank) in a fused all-reduce of a
+// row-parallel forward over `world` ranks; 0 when the geometry cannot take it.
+int tc_reduce_tiles(int format, int M, int N, int K_local, int world) {
+  if (M <= 0 || N <= 0 || K_local <= 0 || world < 1 || N % world || (N / world) % kBlockN) return 0;
+  const TcPlan pl = make_plan(format, M, N, K_local, true);
+  return pl.m_tiles * (pl.n_tiles / world);
+}
+
 // Units of output one rank's fused-gather forward of this geometry announces on every rank
 // (what b200q_gather_wait must be told): output tiles of the tile kernel.
 int tc_output_tiles(int format, int M, int N, int K) {
@@ -1363,7 +1465,8 @@ int launch_forward_tc(const ForwardArgs& a) {
   if (sk_supported(a) && (a.force_streamk || sk_preferred(a.format, a.M, a.N, a.K))) return launch_forward_sk(a);
   // The fused argmax never splits K: it needs the header (counters and row keys) only.
   if (a.argmax && a.M > kMaxArgmaxRows) return B200Q_ERR_UNSUPPORTED;
-  const TcPlan pl = make_plan(a.format, a.M, a.N, a.K, a.argmax);
+  // (nor does the fused all-reduce: a rank's K shard is already a K split)
+  const TcPlan pl = make_plan(a.format, a.M, a.N, a.K, a.argmax || (a.reduce != nullptr && a.reduce->world > 1));
   size_t need = kWsExchangeOffset;
   if (pl.splits > 1) need = kWsPartialOffset + sizeof(float) * static_cast<size_t>(pl.splits) * a.M * a.N;
   if (a.workspace_bytes < need) return B200Q_ERR_WORKSPACE;

@@ -36,6 +36,7 @@ struct ForwardArgs {
   bool argmax;          // y is u64 keys[M], zeroed by the caller: row-wise maximum and its channel
   bool force_streamk;   // B200Q_KERNEL_STREAMK: the persistent stream-K variant or nothing
   const b200q_gather* gather;  // fused all-gather destinations, or null
+  const b200q_reduce* reduce;  // fused all-reduce of a row-parallel forward, or null
   cudaStream_t stream;
 };
 
@@ -60,6 +61,7 @@ bool tc_supported(const ForwardArgs& a);
 size_t tc_workspace_bytes(int format, int M, int N, int K);
 int launch_forward_tc(const ForwardArgs& a);
 int tc_output_tiles(int format, int M, int N, int K);
+int tc_reduce_tiles(int format, int M, int N, int K_local, int world);
 void tc_describe_plan(int format, int M, int N, int K, char* text, size_t size);
 int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream);
 

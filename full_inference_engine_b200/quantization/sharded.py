@@ -205,3 +205,206 @@ class ColumnParallelLinear(nn.Module):
 
     def extra_repr(self) -> str:
         return f"world={self.world}, gather={self.gather}"
+
+
+# ---------------------------------------------------------------------------------------
+# Row-parallel (K-sharded) linears: the pairing of the column-parallel ones above.
+#
+# A column-parallel gate/up (or q/k/v) projection leaves rank r with output columns
+# [r*N/P, (r+1)*N/P) — which are exactly the INPUT columns a row-parallel down (or o)
+# projection needs on rank r.  Each rank then multiplies its activation slice with its K
+# slice of the weights and the partial [M, N] results are summed over the ranks: one exchange
+# per feed-forward instead of a gather after every layer.  The reference has no such path.
+
+def shard_inputs(in_features: int, world: int, rank: int, group_size: int = 1) -> tuple[int, int]:
+    """Input-column range of ``rank``; whole quantization groups, equal shares."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} is not in a world of {world}")
+    if in_features % (world * group_size):
+        raise ValueError(f"in_features {in_features} does not split into {world} shares of whole "
+                         f"groups of {group_size}")
+    share = in_features // world
+    return rank * share, (rank + 1) * share
+
+
+def shard_quantized_linear_inputs(module: nn.Module, rank: int, world: int) -> nn.Module:
+    """A copy of ``module`` holding only this rank's input columns (and their group scales).
+
+    INT4 statistics are per (row, group) and a shard is whole groups, so quantize-then-shard
+    equals shard-then-quantize bit for bit.  INT8 scales are per whole row: shard AFTER
+    quantizing (every rank keeps the full-row scale).  The bias stays on every shard; the
+    row-parallel forward adds it once.
+    """
+    if isinstance(module, W4A16Linear):
+        start, stop = shard_inputs(module.in_features, world, rank, module.group_size)
+        local = W4A16Linear(stop - start, module.out_features, group_size=module.group_size,
+                            bias=False, device="meta")
+        local.packed = module.packed[:, start // 2:stop // 2].contiguous()
+        local.scales = module.scales[:, start // module.group_size:stop // module.group_size].contiguous()
+        local.bias = None if module.bias is None else module.bias.clone()
+        local.reference = module.reference
+        return local
+    if isinstance(module, Int8Linear):
+        start, stop = shard_inputs(module.in_features, world, rank)
+        local = copy.copy(module)
+        nn.Module.__init__(local)
+        local.in_features, local.out_features = stop - start, module.out_features
+        local.reference = module.reference
+        local.register_buffer("qweight", module.qweight[:, start:stop].contiguous())
+        local.register_buffer("scales", module.scales.clone())
+        local.register_buffer("bias", None if module.bias is None else module.bias.clone())
+        return local
+    raise TypeError(f"cannot shard {type(module).__name__}")
+
+
+class SymmetricReduce:
+    """Full ``[rows, N]`` output plus the inbox of partials, both in symmetric memory.
+
+    Creating one is a rendezvous of every rank of ``group``; never inside a graph capture.
+    """
+
+    def __init__(self, rows: int, out_features: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .. import _lib
+
+        group = group if group is not None else dist.group.WORLD
+        world = dist.get_world_size(group)
+        if out_features % world:
+            raise ValueError(f"out_features {out_features} does not divide over {world} ranks")
+        self.tensor = symm_mem.empty((rows, out_features), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        # one 32-bit word per (source rank, row, owned column); zero = "nothing delivered"
+        self.inbox = symm_mem.empty((world, rows, out_features // world), dtype=torch.int32, device=device)
+        self.inbox.zero_()
+        self.inbox_handle = symm_mem.rendezvous(self.inbox, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                       # every inbox is zero before any rank sends
+        self.desc = _lib.Reduce()
+        self.desc.rank, self.desc.world = self.handle.rank, self.handle.world_size
+        for r in range(self.handle.world_size):
+            self.desc.y_peer[r] = self.handle.buffer_ptrs[r]
+            self.desc.signal_peer[r] = self.handle.signal_pad_ptrs[r]
+            self.desc.inbox_peer[r] = self.inbox_handle.buffer_ptrs[r]
+
+    def status(self) -> int:
+        pad = self.handle.get_signal_pad(self.handle.rank, (8,), torch.int64)
+        return int(pad[2].item())
+
+
+def fused_forward_reduce(rows: torch.Tensor, out: SymmetricReduce, *, qweight=None, packed=None,
+                         scales=None, zeros=None, bias=None, group_size: int = 128) -> bool:
+    """This rank's partial of ``rows_local . W_local^T`` reduced over the ranks inside the kernel's
+    epilogue; afterwards ``out.tensor`` holds the full ``[M, N]`` result on every rank.
+
+    ``rows`` is this rank's slice ``[M, K/world]`` of the activations; the weight tensors hold
+    this rank's input columns of ALL ``N`` rows.  Returns False (nothing launched) when the
+    geometry cannot take the fused path.
+    """
+    from .. import _lib
+
+    lib = _lib.library()
+    m, k_local = rows.shape
+    is_w4 = packed is not None
+    n = (packed if is_w4 else qweight).shape[0]
+    world = out.desc.world
+    tiles = lib.b200q_reduce_tiles(4 if is_w4 else 8, m, n, k_local, group_size if is_w4 else 0, world)
+    if tiles <= 0 or m == 0:
+        return False
+    ws = _lib.workspace_for(rows.device, _lib.workspace_bytes(4 if is_w4 else 8, m, n, k_local))
+    stream = _lib.stream_ptr(rows.device)
+    bias_ptr = None if bias is None else bias.data_ptr()
+    with torch.cuda.device(rows.device):
+        if is_w4:
+            layout = _lib.W4_REF_SPLIT_HALF_SYM if zeros is None else _lib.W4_ASYM_ZP_INT32
+            _lib.check(lib.b200q_w4a16_forward_reduce(
+                rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
+                packed.data_ptr(), packed.stride(0) * packed.element_size(), layout,
+                scales.data_ptr(), None if zeros is None else zeros.data_ptr(), group_size, bias_ptr,
+                ctypes.byref(out.desc), out.tensor.stride(0), m, n, k_local,
+                ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                "b200q_w4a16_forward_reduce")
+        else:
+            _lib.check(lib.b200q_w8a16_forward_reduce(
+                rows.data_ptr(), rows.stride(0), _lib.dtype_enum(rows.dtype),
+                qweight.data_ptr(), qweight.stride(0), scales.data_ptr(),
+                _lib.dtype_enum(scales.dtype), bias_ptr,
+                ctypes.byref(out.desc), out.tensor.stride(0), m, n, k_local,
+                ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                "b200q_w8a16_forward_reduce")
+        _lib.check(lib.b200q_reduce_wait(ctypes.byref(out.desc), tiles, stream), "b200q_reduce_wait")
+    return True
+
+
+class RowParallelLinear(nn.Module):
+    """This rank's input-column shard plus the sum over ranks that rebuilds ``[..., N]``.
+
+    ``forward`` takes this rank's SLICE of the activations (``[..., K/world]``).  ``fused=True``
+    (CUDA, NVLink peers) does the sum inside the kernel's epilogue through peer memory; otherwise
+    the local partial (without bias) goes through one ``all_reduce`` and the bias is added once.
+    """
+
+    def __init__(self, local: nn.Module, *, world: int | None = None, group=None, fused: bool = False):
+        super().__init__()
+        self.local = local
+        self.group = group
+        self.world = world if world is not None else dist.get_world_size(group)
+        self.fused = fused
+        self.in_features = local.in_features * self.world
+        self.out_features = local.out_features
+        self._buffers_by_rows: dict = {}
+
+    def _symmetric(self, rows: int, dtype: torch.dtype, device: torch.device) -> SymmetricReduce:
+        key = (rows, dtype)
+        held = self._buffers_by_rows.get(key)
+        if held is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("first fused call for this row count must happen outside "
+                                   "CUDA-graph capture (it allocates symmetric memory)")
+            held = SymmetricReduce(rows, self.out_features, dtype, device, self.group)
+            self._buffers_by_rows[key] = held
+        return held
+
+    def _fused_forward(self, x: torch.Tensor) -> torch.Tensor | None:
+        local = self.local
+        rows = x.reshape(-1, local.in_features)
+        if rows.dtype not in (torch.float16, torch.bfloat16) or rows.device.type != "cuda":
+            return None
+        if getattr(local, "reference", False) or rows.shape[0] == 0:
+            return None
+        if rows.stride(1) != 1 or rows.stride(0) % 8 or rows.data_ptr() % 16:
+            rows = rows.contiguous()
+        out = self._symmetric(rows.shape[0], rows.dtype, rows.device)
+        bias = None if local.bias is None else local.bias.to(rows.dtype).contiguous()
+        if isinstance(local, W4A16Linear):
+            done = fused_forward_reduce(rows, out, packed=local.packed, scales=local.scales, bias=bias,
+                                        group_size=local.group_size)
+        else:
+            done = fused_forward_reduce(rows, out, qweight=local.qweight, scales=local.scales, bias=bias)
+        return out.tensor.reshape(*x.shape[:-1], self.out_features) if done else None
+
+    def reduce_status(self) -> int:
+        status = 0
+        for held in self._buffers_by_rows.values():
+            status |= held.status()
+        return status
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.fused and self.world > 1:
+            out = self._fused_forward(x)
+            if out is not None:
+                return out
+        bias, self.local.bias = self.local.bias, None     # the partial carries no bias
+        try:
+            y = self.local(x)
+        finally:
+            self.local.bias = bias
+        if self.world > 1:
+            y = y.float()                                  # partials are summed in fp32
+            dist.all_reduce(y, group=self.group)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        return y.to(x.dtype)
+
+    def extra_repr(self) -> str:
+        return f"world={self.world}, fused={self.fused}"

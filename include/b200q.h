@@ -283,6 +283,58 @@ int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype,
 int b200q_gather_wait(const b200q_gather* gather, int tiles_per_rank, void* stream);
 
 /*
+ * Fused row-parallel forward + all-reduce (no reference counterpart: the reference is
+ * single-GPU).  The pairing of the column-parallel forward above: rank `rank` of `world`
+ * holds the K_local = K/world INPUT columns [rank*K_local, (rank+1)*K_local) of the
+ * weights (all N rows; for INT4 whole groups, with their scales) and the matching slice
+ * of the activations, which is exactly what a column-parallel gate/up or q/k/v projection
+ * leaves on it, so a feed-forward needs ONE exchange instead of a gather per layer.
+ * Each rank computes a partial [M, N]; the rank that owns a block of N/world output
+ * columns receives the other ranks' partials of those columns in its inbox (peer stores of
+ * self-validating fp32 words: no flag, no collective), adds them in rank order (a fixed
+ * order: results are reproducible), adds the bias, rounds once and stores the finished
+ * tile into the [M, ldy] output of EVERY rank.
+ *   y_peer[r]       peer-mapped base of rank r's full output buffer
+ *   signal_peer[r]  as for b200q_gather (>= 256 bytes, zero-filled once)
+ *   inbox_peer[r]   peer-mapped base of rank r's inbox: world * M * (N/world) 32-bit
+ *                   words, zero-filled once when created; every call leaves it zero
+ * Enqueue b200q_reduce_wait after the forward (same stream) before anything reads y.
+ * Every rank makes the same sequence of calls.  N % world == 0 and (N/world) % 128 == 0;
+ * b200q_reduce_tiles() == 0 means the geometry must use a separate collective.  Bias is
+ * added once, by the owner.  Not with SWIGLU_PAIRS or ARGMAX.
+ */
+typedef struct b200q_reduce {
+  int rank;
+  int world;
+  void* y_peer[8];
+  void* signal_peer[8];
+  void* inbox_peer[8];
+} b200q_reduce;
+
+/* Output tiles one rank owns in such a call (0: not supported fused). */
+int b200q_reduce_tiles(int format, int M, int N, int K_local, int group, int world);
+
+int b200q_w4a16_forward_reduce(const void* x, int64_t ldx, int act_dtype,
+                               const void* packed, int64_t ldw, int layout,
+                               const void* scales, const void* zeros, int group,
+                               const void* bias,
+                               const b200q_reduce* reduce, int64_t ldy,
+                               int M, int N, int K_local,
+                               void* workspace, size_t workspace_bytes,
+                               int flags, void* stream);
+
+int b200q_w8a16_forward_reduce(const void* x, int64_t ldx, int act_dtype,
+                               const int8_t* qweight, int64_t ldw,
+                               const void* scales, int scale_dtype,
+                               const void* bias,
+                               const b200q_reduce* reduce, int64_t ldy,
+                               int M, int N, int K_local,
+                               void* workspace, size_t workspace_bytes,
+                               int flags, void* stream);
+
+int b200q_reduce_wait(const b200q_reduce* reduce, int tiles_per_rank, void* stream);
+
+/*
  * The INT4 forward for callers that have no device memory to give: same
  * arguments and results as b200q_w4a16_forward, minus the workspace.  It has no
  * counterpart in the reference.  It exists for hosts that cannot allocate on the
