@@ -1,7 +1,7 @@
 """Benchmark of the weight-only quantized linear forward on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload all|c1|c2|c3|c4|c5|mlp|head] [--layout asym|ref]
+                    [--workload all|c1|c2|c3|c3fused|c4|c5|mlp|head] [--layout asym|ref]
 
 A *step* is one pass of the hot path over every case of the workload (one forward per
 (format, shape, M) case) on synthetic seeded tensors.  The default workload ``all`` is the
@@ -78,6 +78,8 @@ WORKLOAD_TEXT = {
            "fp16; per_case carries the two-projections-plus-elementwise time beside it",
     "c3": "config 3: 28 x 7 random-init Qwen3-0.6B W8A16 projections, one mixed step of M=144 rows "
           "(16 decode + 128 prefill), fp16, one CUDA graph",
+    "c3fused": "config 3 with q/k/v and gate/up of every layer concatenated along their output rows "
+               "(FusedProjections): 28 x 4 W8A16 launches over the same weights, M=144, fp16, one CUDA graph",
 }
 
 
@@ -152,6 +154,12 @@ def build_cases(workload: str, layout: str) -> list[Case]:
         # one mixed step of a Qwen3-0.6B-shaped model: 16 decode rows + one 128-token chunk
         shapes = {"q": (1024, 2048), "k": (1024, 1024), "v": (1024, 1024), "o": (2048, 1024),
                   "gate": (1024, 3072), "up": (1024, 3072), "down": (3072, 1024)}
+        return [Case(f"L{layer:02d}.{name}", "w8", 144, k, n, torch.float16, cfg="c3")
+                for layer in range(28) for name, (k, n) in shapes.items()]
+    if workload == "c3fused":
+        # the same step with the projections that read the same activations concatenated along
+        # their output rows (q/k/v, gate/up): 4 launches per layer instead of 7, same weight bytes
+        shapes = {"qkv": (1024, 4096), "o": (2048, 1024), "gate_up": (1024, 6144), "down": (3072, 1024)}
         return [Case(f"L{layer:02d}.{name}", "w8", 144, k, n, torch.float16, cfg="c3")
                 for layer in range(28) for name, (k, n) in shapes.items()]
     raise SystemExit(f"unknown workload {workload}")
@@ -539,7 +547,7 @@ def run_b200(args, cases):
         uses[c.wkey] = use_index[-1] + 1
     step_weight_bytes = sum(c.weight_bytes() for c in local_cases)
     variants = max(2, min(96, -(-2 * L2_BYTES // step_weight_bytes)))
-    if args.workload == "c3":
+    if args.workload in ("c3", "c3fused"):
         variants = 1          # 196 distinct matrices, 600 MB per step
     copies_of = {key: n * variants for key, n in uses.items()}
     weight_sets, full_sets = make_weight_sets(cases, copies_of, device, rank, world, keep_full=True)
@@ -782,7 +790,7 @@ def run_b200(args, cases):
     # buffers that none is still in L2 when it comes round again
     per_case = []
     for i, case in enumerate(local_cases):
-        if args.workload == "c3":
+        if args.workload in ("c3", "c3fused"):
             if not case.name.startswith("L00."):
                 continue
             # the same projection of all 28 layers: 28 distinct weight buffers in rotation
@@ -863,6 +871,14 @@ def run_b200(args, cases):
     clocks = sampler.stop()
     note("per-case timing done")
 
+    # ---- multi-rank only: a feed-forward's two projections (INT4 gate/up 4096 -> 12288, down
+    # 12288 -> 4096) joined two ways: column-parallel + all-gather after each, against
+    # column-parallel without a gather feeding a row-parallel down with the all-reduce fused
+    # into its epilogue (one exchange).  Outside the timed region; device time, max over ranks.
+    ffn_pairing = None
+    if world > 1 and args.workload in ("all", "c2", "c5"):
+        ffn_pairing = measure_ffn_pairing(args, device, rank, world, barrier, max_over_ranks, note)
+
     status = _lib.library().b200q_workspace_status(_lib.workspace_for(device, 256).data_ptr(), None)
     if fused_out is not None:      # a bounded wait of the fused gather protocol expired somewhere
         status = status or (7 if any(o.status() for o in fused_out) else 0)
@@ -871,7 +887,7 @@ def run_b200(args, cases):
     if rank == 0:
         total_bytes = sum(c.bytes for c in cases)          # whole job, all ranks
         total_flops = sum(c.flops for c in cases)
-        scale = 28 if args.workload == "c3" else 1
+        scale = 28 if args.workload in ("c3", "c3fused") else 1
         timed = [r for r in per_case if "_sec" in r]
         step_sec = sum(r["_sec"] for r in timed) * scale
 
@@ -943,6 +959,7 @@ def run_b200(args, cases):
                 "per_case": "per_case[*].us is the sharded GEMM alone, fused_gather_us / nccl_gather_us "
                             "the GEMM with that all-gather"},
             "gather_parity": gather_parity,
+            "ffn_pairing": ffn_pairing,
             "device_status": status,
         }
         if world == 1:
@@ -970,6 +987,68 @@ def run_b200(args, cases):
         sys.exit(exit_code)
 
 
+def measure_ffn_pairing(args, device, rank, world, barrier, max_over_ranks, note):
+    import torch.distributed as dist
+
+    from full_inference_engine_b200.kernels import w4a16_format as w4
+    from full_inference_engine_b200.kernels import w4a16_linear
+    from full_inference_engine_b200.quantization.sharded import (
+        SymmetricOutput, SymmetricReduce, fused_forward_gather, fused_forward_reduce)
+
+    hidden, inter = 4096, 12288
+    gen = torch.Generator(device=device).manual_seed(77)
+    up_w = torch.randn(inter, hidden, generator=gen, device=device) * 0.02
+    down_w = torch.randn(hidden, inter, generator=gen, device=device) * 0.02
+    rows_up, rows_down, k_share = inter // world, hidden // world, inter // world
+    copies = 6
+    up_col = [w4.quantize_weight_w4_grouped(up_w[rank * rows_up:(rank + 1) * rows_up])]
+    down_col = [w4.quantize_weight_w4_grouped(down_w[rank * rows_down:(rank + 1) * rows_down])]
+    down_row = [w4.quantize_weight_w4_grouped(down_w[:, rank * k_share:(rank + 1) * k_share].contiguous())]
+    down_full = w4.quantize_weight_w4_grouped(down_w)
+    up_full = w4.quantize_weight_w4_grouped(up_w)
+    del up_w, down_w
+    for sets in (up_col, down_col, down_row):
+        sets += [tuple(t.clone() for t in sets[0]) for _ in range(copies - 1)]
+    out = []
+    for m in (16, 512, 4096):
+        x = torch.randn(m, hidden, generator=gen, device=device).half()
+        dist.broadcast(x, 0)
+        mid_buf = SymmetricOutput(m, inter, torch.float16, device)
+        y_buf = SymmetricOutput(m, hidden, torch.float16, device)
+        red_buf = SymmetricReduce(m, hidden, torch.float16, device)
+
+        def two_gathers(i):
+            fused_forward_gather(x, mid_buf, packed=up_col[i][0], scales=up_col[i][1])
+            fused_forward_gather(mid_buf.tensor, y_buf, packed=down_col[i][0], scales=down_col[i][1])
+            return y_buf.tensor
+
+        def paired(i):
+            mid = w4a16_linear.w4a16_linear(x, up_col[i][0], up_col[i][1], static_weights=True)
+            fused_forward_reduce(mid, red_buf, packed=down_row[i][0], scales=down_row[i][1])
+            return red_buf.tensor
+
+        want = w4a16_linear.w4a16_linear(w4a16_linear.w4a16_linear(x, up_full[0], up_full[1]),
+                                         down_full[0], down_full[1]).float()
+        entry = {"M": m}
+        for label, fn in (("two_gathers_us", two_gathers), ("paired_one_exchange_us", paired)):
+            got = fn(0).float()
+            entry[label.replace("_us", "_max_rel_err")] = round(
+                float((got - want).abs().max() / want.abs().max()), 5)
+            fn(1)
+            torch.cuda.synchronize()
+            barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(copies):
+                    fn(i)
+            entry[label] = round(max_over_ranks(time_graph(g, copies)) * 1e6, 2)
+            del g
+        out.append(entry)
+        note(f"ffn pairing: {entry}")
+        del mid_buf, y_buf, red_buf
+    return {"shapes": "INT4 g128 4096 -> 12288 -> 4096, fp16", "cases": out}
+
+
 def run_profile(args, cases):
     """Plain eager launches, one weight buffer per launch: the command ncu wraps."""
     torch.cuda.set_device(0)
@@ -994,7 +1073,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c4", "c5", "mlp", "head"])
+    ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c3fused", "c4", "c5", "mlp", "head"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],

@@ -195,3 +195,25 @@ def test_streaming_loader_onto_the_gpu_matches_install(tmp_path):
     head = loaded.get_output_embeddings()
     assert isinstance(head, W4A16Linear) and head.loaded and report.by_kind["lm_head"] == 1
     assert torch.isfinite(_logits(loaded, ids)).all()
+
+
+def test_fused_qkv_runs_one_launch_for_three_projections():
+    """q/k/v concatenated into one weight-only linear: two launches fewer per layer, and the
+    logits stay within rounding of the unfused model's (same kernel arithmetic per channel)."""
+    from full_inference_engine_b200.quantization import install_fused_qkv, uninstall_fused_qkv
+
+    shape = (256, 512, 4, 2, 64, 512)
+    model = _model(*shape, dtype=torch.float16).cuda()
+    install_w4a16(model, group_size=128)
+    ids = torch.randint(0, shape[-1], (1, 24), device="cuda")
+    expected = _logits(model, ids).float()
+    assert install_fused_qkv(model) == 2
+    before = _lib.launch_count()
+    actual = _logits(model, ids).float()
+    assert _lib.launch_count() - before == 15 - 2 * 2
+    torch.testing.assert_close(actual, expected, rtol=2e-2, atol=1e-1)
+    with reference_mode(model):
+        reference = _logits(model, ids).float()
+    torch.testing.assert_close(actual, reference, rtol=2e-2, atol=1e-1)
+    assert uninstall_fused_qkv(model) == 2
+    torch.testing.assert_close(_logits(model, ids).float(), expected, rtol=0, atol=0)
