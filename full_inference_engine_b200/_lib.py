@@ -37,6 +37,11 @@ _SIGNATURES = {
     "b200q_last_error": (ctypes.c_char_p, []),
     "b200q_quantize_w8_per_channel": (_c_int, [_c_void_p, _c_int, _c_i64, _c_int, _c_int, _c_int,
                                                _c_void_p, _c_void_p, _c_void_p]),
+    "b200q_quantize_rows_int8": (_c_int, [_c_void_p, _c_i64, _c_int, _c_int, _c_int, _c_void_p, _c_i64,
+                                          _c_void_p, _c_void_p]),
+    "b200q_w8a8_forward": (_c_int, [_c_void_p, _c_i64, _c_void_p, _c_void_p, _c_i64, _c_void_p, _c_int,
+                                    _c_void_p, _c_i64, _c_int, _c_int, _c_int, _c_int,
+                                    _c_void_p, _c_size, _c_void_p]),
     "b200q_quantize_w4_grouped": (_c_int, [_c_void_p, _c_int, _c_i64, _c_int, _c_int, _c_int, _c_int,
                                            _c_void_p, _c_void_p, _c_void_p, _c_void_p]),
     "b200q_w4_dequant": (_c_int, [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,

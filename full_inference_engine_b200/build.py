@@ -19,7 +19,7 @@ CSRC = os.path.join(PACKAGE_DIR, "csrc")
 INCLUDE = os.path.join(REPO_ROOT, "include")
 LIB_DIR = os.path.join(PACKAGE_DIR, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libb200q.so")
-SOURCES = ("api.cu", "quantize.cu", "gemv_simt.cu", "gemm_tc.cu", "gemm_sk.cu", "static_scratch.cu")
+SOURCES = ("api.cu", "quantize.cu", "gemv_simt.cu", "gemm_tc.cu", "gemm_sk.cu", "gemm_i8.cu", "static_scratch.cu")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

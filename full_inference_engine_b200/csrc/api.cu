@@ -97,6 +97,26 @@ int b200q_quantize_w8_per_channel(const void* w, int w_dtype, int64_t ldw, int N
   return launch_quantize_w8(w, w_dtype, ldw, N, K, mode, q, scales, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_quantize_rows_int8(const void* x, int64_t ldx, int act_dtype, int M, int K, int8_t* q, int64_t ldq,
+                             float* scales, void* stream) {
+  if (!x || !q || !scales || M < 0 || K <= 0 || ldx < K || ldq < K) return B200Q_ERR_INVALID;
+  if (M == 0) return B200Q_OK;
+  return launch_quantize_rows_int8(x, ldx, act_dtype, M, K, q, ldq, scales, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_w8a8_forward(const int8_t* qx, int64_t ldq, const float* act_scales, const int8_t* qweight, int64_t ldw,
+                       const void* weight_scales, int weight_scale_dtype, void* y, int64_t ldy, int out_dtype, int M,
+                       int N, int K, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!qx || !act_scales || !qweight || !weight_scales || !y) return B200Q_ERR_INVALID;
+  if (M < 0 || N < 0 || K <= 0 || ldq < K || ldw < K || ldy < N) return B200Q_ERR_INVALID;
+  if (weight_scale_dtype != B200Q_F16 && weight_scale_dtype != B200Q_F32) return B200Q_ERR_INVALID;
+  if (out_dtype != B200Q_F16 && out_dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (workspace != nullptr && workspace_bytes < 256) return B200Q_ERR_WORKSPACE;
+  if (M == 0 || N == 0) return B200Q_OK;
+  return launch_forward_w8a8(qx, ldq, act_scales, qweight, ldw, weight_scales, weight_scale_dtype, y, ldy, out_dtype,
+                             M, N, K, static_cast<unsigned*>(workspace), static_cast<cudaStream_t>(stream));
+}
+
 int b200q_quantize_w4_grouped(const void* w, int w_dtype, int64_t ldw, int N, int K, int group,
                               int layout, void* packed, void* scales, void* zeros, void* stream) {
   if (!w || !packed || !scales || N < 0 || K <= 0 || ldw < K) return B200Q_ERR_INVALID;

@@ -65,4 +65,11 @@ int tc_reduce_tiles(int format, int M, int N, int K_local, int world);
 void tc_describe_plan(int format, int M, int N, int K, char* text, size_t size);
 int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream);
 
+// gemm_i8.cu — W8A8: per-row activation quantisation and the int8 x int8 tensor-core GEMM.
+int launch_quantize_rows_int8(const void* x, int64_t ldx, int act_dtype, int M, int K, int8_t* q, int64_t ldq,
+                              float* scales, cudaStream_t stream);
+int launch_forward_w8a8(const int8_t* qx, int64_t ldq, const float* a_scales, const int8_t* qw, int64_t ldw,
+                        const void* w_scales, int w_scale_dtype, void* y, int64_t ldy, int out_dtype, int M, int N,
+                        int K, unsigned* status, cudaStream_t stream);
+
 }  // namespace b200q

@@ -132,6 +132,37 @@ int b200q_quantize_w8_per_channel(const void* w, int w_dtype, int64_t ldw,
                                   int8_t* q, void* scales, void* stream);
 
 /*
+ * W8A8 linear (engine/kernels/w8a8_linear.py:35-50), in two calls so that the quantised
+ * activations can be reused by every projection that reads the same input.
+ *
+ * b200q_quantize_rows_int8 is the reference's per-row dynamic quantisation (lines 43-45):
+ *   scales[m] = max_k |float(x[m,k])| clamp_min 1e-8, / 127      (fp32, IEEE division)
+ *   q[m,k]    = clamp(rint(float(x[m,k]) / scales[m]), -127, 127)
+ *     x       [M, ldx] of act_dtype (f16 / bf16 / f32)
+ *     q       [M, ldq] int8; for b200q_w8a8_forward q must be 16-byte aligned with ldq % 16 == 0
+ *     scales  [M] fp32
+ *
+ * b200q_w8a8_forward replaces torch._int_mm and the scaling of lines 46-48:
+ *   y[m,n] = out_dtype( (float(sum_k qx[m,k] * qweight[n,k]) * act_scales[m]) * float(weight_scales[n]) )
+ * with the sum exact in int32 (tcgen05.mma kind::i8).
+ *     qweight        [N, ldw] int8 row-major (the [N,K] matrix quantize_weight_per_channel
+ *                    returns, NOT the transposed copy pack_w8a8_weight makes for cuBLAS),
+ *                    16-byte aligned, ldw % 16 == 0
+ *     weight_scales  [N] f16 or f32
+ *     y              [M, ldy] f16 or bf16
+ *     workspace      optional: when non-null (>= 256 bytes) an expired device-side wait is
+ *                    recorded in its status word; no other scratch is used
+ * K must be a multiple of 16 (B200Q_ERR_UNSUPPORTED otherwise); any M and N.
+ */
+int b200q_quantize_rows_int8(const void* x, int64_t ldx, int act_dtype, int M, int K,
+                             int8_t* q, int64_t ldq, float* scales, void* stream);
+int b200q_w8a8_forward(const int8_t* qx, int64_t ldq, const float* act_scales,
+                       const int8_t* qweight, int64_t ldw,
+                       const void* weight_scales, int weight_scale_dtype,
+                       void* y, int64_t ldy, int out_dtype, int M, int N, int K,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Quantize [N,K] weights to 4 bits in groups of `group` along K and pack.
  * REF layout replaces quantize_weight_w4_grouped
  * (engine/kernels/w4a16_format.py:32-50) bit for bit; `zeros` must be NULL.

@@ -11,6 +11,12 @@ tests (``tests/kernels/test_w4a16_linear.py:18-70``) and (b) golden vectors prod
 importing the reference itself (``tests/golden/make_golden.py`` holds the generator,
 ``tests/golden/*.npz`` its output).
 
+The W8A8 functions are pinned by ``tests/golden/reference_w8a8.npz``: outputs of the
+reference's own ``w8a8_linear`` executed on CPU tensors (``tests/golden/make_golden_w8a8.py``),
+which the oracle reproduces bit for bit in its ``scalar_division="cpu"`` form.  The one step
+where torch's CUDA arithmetic differs from its CPU arithmetic (tensor / Python scalar) is
+checked on the GPU against the same torch expressions the reference evaluates.
+
 The asymmetric 4-bit layout (``*_asym`` functions) has no counterpart in the reference:
 **parity unpinned** for it.  Its definition is frozen here and in ``include/b200q.h``.
 
@@ -145,6 +151,50 @@ def unpack_w4_asym(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, in
     q = ((words >> shifts) & 0xF).reshape(n, in_features // group_size, group_size)
     centred = (q.astype(np.float32) - zeros.astype(np.float32)[..., None]).astype(np.float16)
     return (centred * scales.astype(np.float16)[..., None]).reshape(n, in_features)
+
+
+# --------------------------------------------------------------------------- W8A8
+def quantize_rows_int8(x: np.ndarray, scalar_division: str = "cuda") -> tuple[np.ndarray, np.ndarray]:
+    """engine/kernels/w8a8_linear.py:43-44 — per-row dynamic activation quantisation:
+    ``scale = amax(|x.float()|).clamp_min(1e-8) / 127.0`` and
+    ``q = round(x.float() / scale).clamp(-127, 127).to(int8)``.  Returns (int8 [M,K], fp32 [M]).
+
+    ``/ 127.0`` divides a tensor by a Python scalar.  torch's CUDA kernel evaluates that as a
+    multiplication by the fp32 reciprocal (``scalar_division="cuda"``: the reference's
+    arithmetic, since its function only accepts CUDA tensors); torch's CPU kernel divides
+    (``"cpu"``: what the CPU-generated golden vectors hold).  The two scales differ by at most
+    one ulp.  ``x / scale`` is tensor by tensor, an IEEE division on both devices."""
+    if scalar_division not in ("cuda", "cpu"):
+        raise ValueError("scalar_division must be 'cuda' or 'cpu'")
+    x32 = x.astype(np.float32)
+    peak = np.maximum(np.abs(x32).max(axis=1, keepdims=True), np.float32(1e-8)) if x32.shape[1] else \
+        np.full((x32.shape[0], 1), 1e-8, np.float32)
+    if scalar_division == "cuda":
+        scales = (peak * (np.float32(1.0) / np.float32(127.0))).astype(np.float32)
+    else:
+        scales = (peak / np.float32(127.0)).astype(np.float32)
+    q = np.clip(np.rint(x32 / scales), -127, 127).astype(np.int8)
+    return q, scales[:, 0]
+
+
+def round_to_bf16(values: np.ndarray) -> np.ndarray:
+    """fp32 -> bf16 by round-to-nearest-even, returned as the exactly representable fp32."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return rounded.view(np.float32)
+
+
+def w8a8_linear(x: np.ndarray, qweight: np.ndarray, weight_scales: np.ndarray, bf16: bool = False,
+                scalar_division: str = "cuda") -> np.ndarray:
+    """engine/kernels/w8a8_linear.py:35-50 for ``qweight`` [N,K] int8 (the reference passes its
+    transpose): exact integer sums, then ``(acc.float() * act_scale) * weight_scale.float()`` and
+    one rounding to the activation dtype (fp16, or bf16 returned as fp32 values)."""
+    q, a_scales = quantize_rows_int8(x, scalar_division)
+    # float64 carries these sums exactly (every partial sum is an integer below 2**53)
+    acc = (q.astype(np.float64) @ qweight.astype(np.float64).T).astype(np.int64)
+    assert np.abs(acc).max(initial=0) < 2 ** 31
+    y = (acc.astype(np.int32).astype(np.float32) * a_scales[:, None]) * weight_scales.astype(np.float32)[None, :]
+    return round_to_bf16(y) if bf16 else y.astype(np.float16)
 
 
 # --------------------------------------------------------------------------- ground truth

@@ -34,7 +34,7 @@ def _device_loops(code: str):
 
 def test_sources_were_found():
     names = {p.name for p in SOURCES}
-    assert {"gemm_tc.cu", "gemm_sk.cu", "gemv_simt.cu", "quantize.cu", "api.cu", "ptx.cuh"} <= names
+    assert {"gemm_tc.cu", "gemm_sk.cu", "gemm_i8.cu", "gemv_simt.cu", "quantize.cu", "api.cu", "ptx.cuh"} <= names
 
 
 @pytest.mark.parametrize("path", SOURCES, ids=lambda p: p.name)
@@ -90,13 +90,13 @@ def test_wait_helpers_have_the_documented_bounds():
     assert re.search(r"for\s*\(uint32_t i = 0; i < \(1u << 22\); \+\+i\)", common), "poll_at_least lost its bound"
 
 
-@pytest.mark.parametrize("name", ["gemm_tc.cu", "gemm_sk.cu"])
+@pytest.mark.parametrize("name", ["gemm_tc.cu", "gemm_sk.cu", "gemm_i8.cu"])
 def test_tensor_memory_is_always_released(name):
     """Every kernel that allocates TMEM frees it on its single exit path, after a block-wide
     barrier that every role reaches (no early `return` inside the kernel body)."""
     code = _code(CSRC / name)
     assert code.count("tmem_alloc(") == code.count("tmem_dealloc("), f"{name}: alloc/dealloc mismatch"
-    for kernel in re.finditer(r"__global__ void[^{]*?wq_gemm_\w+_kernel\([^)]*\)\s*\{", code, flags=re.S):
+    for kernel in re.finditer(r"__global__ void[^{]*?(?:wq_gemm_\w+|w8a8_gemm)_kernel\([^)]*\)\s*\{", code, flags=re.S):
         depth, i = 1, kernel.end()
         while depth and i < len(code):
             depth += {"{": 1, "}": -1}.get(code[i], 0)
@@ -107,7 +107,7 @@ def test_tensor_memory_is_always_released(name):
         assert "tmem_dealloc(" in tail, f"{name}: TMEM is not freed after the final barrier"
 
 
-@pytest.mark.parametrize("name", ["gemm_tc.cu", "gemm_sk.cu"])
+@pytest.mark.parametrize("name", ["gemm_tc.cu", "gemm_sk.cu", "gemm_i8.cu"])
 def test_tma_loads_start_on_16_byte_boundaries(name):
     """The innermost coordinate of every tiled load is the literal 0 (whole 64-byte / 128-byte
     rows) or a multiple of eight 2-byte elements (the scale chunks), and tile stores use a
@@ -117,11 +117,11 @@ def test_tma_loads_start_on_16_byte_boundaries(name):
     assert loads, f"{name}: no TMA loads found"
     for args in loads:
         parts = [a.strip() for a in re.split(r",(?![^()]*\))", args)]
-        assert parts[3] == "0" or re.fullmatch(r"\(\w+ >> 3\) \* 8", parts[3]), \
+        assert parts[3] == "0" or re.fullmatch(r"\(\w+ >> 3\) \* 8|kb \* 128", parts[3]), \
             f"{name}: TMA load with inner coordinate {parts[3]!r}"
     for args in re.findall(r"tma_store_3d\(([^;]*?)\);", code, flags=re.S):
         parts = [a.strip() for a in re.split(r",(?![^()]*\))", args)]
-        assert re.fullmatch(r"n_tile \* tile_out", parts[2]), f"{name}: TMA store inner coordinate {parts[2]!r}"
+        assert re.fullmatch(r"n_tile \* (tile_out|kBlockN)", parts[2]), f"{name}: TMA store inner coordinate {parts[2]!r}"
 
 
 def test_header_symbols_match_the_binding_table():

@@ -6,6 +6,8 @@ Every array in ``tests/golden/reference_vectors.npz`` was produced by the refere
 
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -154,3 +156,43 @@ def test_asym_layout_roundtrip_and_nibble_order():
     t = torch.from_numpy
     assert torch.equal(cpu_path.unpack_w4_asym(t(packed), t(scales), t(zeros), 128),
                        t(oracle.unpack_w4_asym(packed, scales, zeros, 128)))
+
+
+# --------------------------------------------------------------------------- W8A8
+W8A8 = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_w8a8.npz"))
+W8A8_CASES = sorted({key.split(".")[0] for key in W8A8.files})
+
+
+@pytest.mark.parametrize("name", W8A8_CASES)
+def test_w8a8_oracle_reproduces_the_reference_bit_for_bit(name):
+    """The numpy restatement against outputs of the reference's w8a8_linear run on CPU tensors
+    (engine/kernels/w8a8_linear.py:35-50)."""
+    x, qweight, scales, y = (W8A8[f"{name}.{part}"] for part in ("x", "qweight", "scales", "y"))
+    bf16 = bool(W8A8[f"{name}.meta"][4])
+    got = oracle.w8a8_linear(x, qweight, scales, bf16=bf16, scalar_division="cpu")
+    assert got.shape == y.shape
+    assert np.array_equal(got.astype(np.float32), y.astype(np.float32))
+
+
+def test_w8a8_row_quantiser_properties():
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((7, 96)).astype(np.float16)
+    x[3] = 0
+    q, scales = oracle.quantize_rows_int8(x, "cpu")
+    assert q.dtype == np.int8 and scales.dtype == np.float32
+    assert np.abs(q).max() == 127 and not q[3].any()
+    assert scales[3] == np.float32(1e-8) / np.float32(127.0)
+    rows = np.abs(x.astype(np.float32)).max(axis=1)
+    assert np.array_equal(scales[rows > 0], (rows[rows > 0] / np.float32(127.0)).astype(np.float32))
+    # the CUDA rule multiplies by the rounded reciprocal: at most one ulp away, same integers almost always
+    q_cuda, scales_cuda = oracle.quantize_rows_int8(x, "cuda")
+    ulps = np.abs(scales.view(np.int32).astype(np.int64) - scales_cuda.view(np.int32).astype(np.int64))
+    assert ulps.max() <= 1
+    assert np.abs(q.astype(np.int16) - q_cuda.astype(np.int16)).max() <= 1
+
+
+def test_bf16_rounding_helper_is_round_to_nearest_even():
+    import torch
+    values = np.random.default_rng(6).standard_normal(4096).astype(np.float32) * 1e3
+    want = torch.from_numpy(values).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(oracle.round_to_bf16(values), want)
