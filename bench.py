@@ -1,7 +1,7 @@
 """Benchmark of the weight-only quantized linear forward on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload all|c1|c2|c3|c3fused|c4|c5|mlp|head] [--layout asym|ref]
+                    [--workload all|c1|c2|c3|c3fused|c4|c5|mlp|head|w8a8] [--layout asym|ref]
 
 A *step* is one pass of the hot path over every case of the workload (one forward per
 (format, shape, M) case) on synthetic seeded tensors.  The default workload ``all`` is the
@@ -45,6 +45,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 METRIC = "W8A16/INT4 GEMM TFLOP/s and HBM GB/s vs M (1-4096), Qwen3-8B shapes"
@@ -1049,6 +1050,129 @@ def measure_ffn_pairing(args, device, rank, world, barrier, max_over_ranks, note
     return {"shapes": "INT4 g128 4096 -> 12288 -> 4096, fp16", "cases": out}
 
 
+# --------------------------------------------------------------------------- W8A8 prefill
+W8A8_SHAPES = [("gate_up", 2048, 22016), ("down", 11008, 2048), ("qkv", 2048, 2560), ("o", 2048, 2048)]
+W8A8_TOKENS = 4096
+
+
+def run_w8a8(args):
+    """The W8A8 linear (row quantiser + int8 tensor-core GEMM) on the four projection shapes of a
+    Qwen2.5-3B layer at 4096 tokens.  One step = quantise + GEMM for each shape.  The roofline
+    entry is compute-bound; its peak is cuBLAS's int8 GEMM (torch._int_mm) on the same shapes,
+    timed in this run, because the measured-peaks file has no int8 figure."""
+    m = W8A8_TOKENS
+    ops = sum(2.0 * m * k * n for _, k, n in W8A8_SHAPES)
+    config = {"workload": f"w8a8 prefill: {m} tokens x Qwen2.5-3B layer projections "
+                          + ", ".join(f"{name} {n}x{k}" for name, k, n in W8A8_SHAPES),
+              "activations": "fp16, per-row dynamic int8", "weights": "int8 per-channel, fp16 scales",
+              "l2": "operands and outputs of one step exceed L2 (360 MB)"}
+    base = {"metric": "w8a8_linear_int8_throughput", "unit": "TOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "s8", "data": "synthetic", "config": config}
+    gen = np.random.default_rng(8)
+    if args.impl == "reference":
+        from oracle import wq_oracle as oracle
+        rows = 64                                           # bounded sample: 64 of the 4096 tokens
+        xs = {name: gen.standard_normal((rows, k)).astype(np.float16) for name, k, n in W8A8_SHAPES}
+        ws = {name: gen.integers(-127, 128, size=(n, k), dtype=np.int8) for name, k, n in W8A8_SHAPES}
+        sc = {name: (gen.random(n) * 0.01).astype(np.float16) for name, k, n in W8A8_SHAPES}
+        def step():
+            for name, _, _ in W8A8_SHAPES:
+                oracle.w8a8_linear(xs[name], ws[name], sc[name])
+        for _ in range(max(1, min(args.warmup, 2))):
+            step()
+        steps = max(1, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        seconds = (time.perf_counter() - t0) / steps
+        value = ops * rows / m / seconds / 1e12
+        cores = os.cpu_count() or 1
+        line = dict(base, impl="reference", value=round(value, 5), ms_per_step=round(seconds * 1e3 * m / rows, 2),
+                    cpu_baseline={"value": round(value, 5), "unit": "TOP/s", "cores": cores, "kind": "port",
+                                  "sample": f"{rows} of {m} tokens per shape, {steps} timed passes, numpy/BLAS threads"},
+                    e2e={"value": round(value, 5), "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        line["steps"] = steps
+        print(json.dumps(line))
+        return
+    from full_inference_engine_b200 import _lib
+    from full_inference_engine_b200.kernels import w8a8_linear as w8a8
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    tensors = {}
+    for name, k, n in W8A8_SHAPES:
+        x_host = torch.from_numpy(gen.standard_normal((m, k)).astype(np.float16)).pin_memory()
+        qw = torch.from_numpy(gen.integers(-127, 128, size=(n, k), dtype=np.int8)).to(device)
+        sc = torch.from_numpy((gen.random(n) * 0.01).astype(np.float16)).to(device)
+        tensors[name] = (x_host, x_host.to(device), w8a8.pack_w8a8_weight(qw), sc, qw.t().contiguous())
+    def step():
+        return [w8a8.w8a8_linear(x, packed, sc) for _, x, packed, sc, _ in tensors.values()]
+    def timed(fn, steps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps / 1e3
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches_before = _lib.launch_count()
+    seconds = timed(step, args.steps)
+    launches = _lib.launch_count() - launches_before
+    clocks = sampler.stop()
+    # the integer GEMM alone, and cuBLAS's on the same operands (the measured int8 peak)
+    quantised = {name: w8a8.quantize_activations_per_row(t[1]) for name, t in tensors.items()}
+    def gemm_only():
+        for name, (_, _, packed, sc, _) in tensors.items():
+            w8a8.w8a8_linear_prequantized(*quantised[name], packed, sc, torch.float16)
+    def cublas_only():
+        for name, (_, _, _, _, ref_packed) in tensors.items():
+            torch._int_mm(quantised[name][0], ref_packed)
+    def quantise_only():
+        for _, x, _, _, _ in tensors.values():
+            w8a8.quantize_activations_per_row(x)
+    def reference_pipeline():
+        out = []
+        for name, (_, x, _, sc, ref_packed) in tensors.items():
+            a = x.float().abs().amax(dim=1, keepdim=True).clamp_min(1e-8) / 127.0
+            q = torch.round(x.float() / a).clamp(-127, 127).to(torch.int8).contiguous()
+            out.append((torch._int_mm(q, ref_packed).float() * a * sc.float()[None, :]).to(x.dtype))
+        return out
+    for fn in (gemm_only, cublas_only, quantise_only, reference_pipeline):
+        for _ in range(3):
+            fn()
+    t_gemm, t_cublas = timed(gemm_only, args.steps), timed(cublas_only, args.steps)
+    t_quant, t_ref = timed(quantise_only, args.steps), timed(reference_pipeline, max(3, args.steps // 5))
+    # end to end: activations from pinned host memory, results back to the host
+    outs_host = [torch.empty((m, n), dtype=torch.float16).pin_memory() for _, _, n in W8A8_SHAPES]
+    def e2e_step():
+        for (x_host, x_dev, packed, sc, _), out in zip(tensors.values(), outs_host):
+            x_dev.copy_(x_host, non_blocking=True)
+            out.copy_(w8a8.w8a8_linear(x_dev, packed, sc), non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    t_e2e = timed(e2e_step, max(3, args.steps // 5))
+    h2d = sum(t[0].numel() * 2 for t in tensors.values())
+    d2h = sum(o.numel() * 2 for o in outs_host)
+    peak = ops / t_cublas / 1e12
+    line = dict(base, value=round(ops / seconds / 1e12, 2), ms_per_step=round(seconds * 1e3, 4),
+                e2e={"value": round(ops / t_e2e / 1e12, 2), "unit": "TOP/s", "h2d_bytes_per_step": h2d,
+                     "d2h_bytes_per_step": d2h},
+                gpu_launches=int(launches), clocks=clocks,
+                roofline={"bound": "tensor", "kernel": "w8a8_gemm_kernel", "achieved": round(ops / t_gemm / 1e12, 2),
+                          "peak": round(peak, 2), "unit": "TOP/s", "frac": round(t_cublas / t_gemm, 4),
+                          "peak_source": "cuBLAS int8 GEMM (torch._int_mm) on the same operands, timed in this run",
+                          "traffic": None},
+                phases={"quantise_ms": round(t_quant * 1e3, 4), "gemm_ms": round(t_gemm * 1e3, 4),
+                        "cublas_int_mm_ms": round(t_cublas * 1e3, 4),
+                        "torch_reference_pipeline_ms": round(t_ref * 1e3, 4)})
+    print(json.dumps(line))
+
+
 def run_profile(args, cases):
     """Plain eager launches, one weight buffer per launch: the command ncu wraps."""
     torch.cuda.set_device(0)
@@ -1073,7 +1197,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c3fused", "c4", "c5", "mlp", "head"])
+    ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c3fused", "c4", "c5", "mlp", "head", "w8a8"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
@@ -1082,6 +1206,11 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="eager launches of the selected cases only (for ncu): no graphs, no e2e, no CPU leg")
     args = ap.parse_args()
+    if args.workload == "w8a8":
+        if args.gpus > 1:
+            raise SystemExit("the w8a8 workload is single-GPU")
+        run_w8a8(args)
+        return
     cases = build_cases(args.workload, args.layout)
     if args.cases:
         wanted = [w for w in args.cases.split(",") if w]

@@ -176,6 +176,7 @@ def require_cuda(tensor: torch.Tensor, what: str) -> None:
 _WORKSPACES: dict[int, torch.Tensor] = {}
 _RETIRED: list[torch.Tensor] = []
 _GRANULE = 8 << 20
+WORKSPACE_GRANULE = _GRANULE
 
 
 def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -196,6 +197,14 @@ def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def workspace_bytes(fmt: int, m: int, n: int, k: int) -> int:
     return int(library().b200q_workspace_bytes(fmt, m, n, k))
+
+
+def max_workspace_bytes(fmt: int, max_rows: int, n: int, k: int) -> int:
+    """Largest workspace any token count up to ``max_rows`` needs for an [n, k] projection
+    (split-K is deepest at middling token counts, so the largest M is not the worst case)."""
+    rows = sorted({m for m in (1, 16, 32, 48, 64, 96, 128, 192, 256, 384, 512, 1024, 2048, 4096, 8192)
+                   if m <= max_rows} | {max(1, max_rows)})
+    return max(workspace_bytes(fmt, m, n, k) for m in rows)
 
 
 def describe_plan(fmt: int, m: int, n: int, k: int, layout: int = W4_REF_SPLIT_HALF_SYM,

@@ -309,13 +309,93 @@ __global__ void __launch_bounds__(256) quantize_rows_int8_kernel(const T* __rest
   }
 }
 
+// The same for 16-bit activations with 16-byte aligned rows: eight values per load, the row kept
+// in registers between the two passes (rows longer than 256 x 8 x kHeld values re-read the
+// rest, which the L2 still holds), eight int8 per store.
+constexpr int kQuantHeld = 6;
+
+template <typename T>
+__device__ __forceinline__ float2 pair_to_float2(uint32_t w);
+template <>
+__device__ __forceinline__ float2 pair_to_float2<__half>(uint32_t w) {
+  return __half22float2(as_h2(w));
+}
+template <>
+__device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
+__device__ __forceinline__ uint32_t quantise4(float a, float b, float c, float d, float scale) {
+  auto one = [scale](float v) {
+    return static_cast<uint32_t>(static_cast<int>(fminf(fmaxf(rintf(__fdiv_rn(v, scale)), -127.0f), 127.0f))) & 0xFFu;
+  };
+  return one(a) | (one(b) << 8) | (one(c) << 16) | (one(d) << 24);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_rows_int8_vec_kernel(const T* __restrict__ x, int64_t ldx, int K,
+                                                                     int8_t* __restrict__ q, int64_t ldq,
+                                                                     float* __restrict__ scales) {
+  const int m = blockIdx.x;
+  const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * ldx);
+  const int vecs = K / 8;
+  uint4 held[kQuantHeld];
+  float peak = 0.0f;
+  auto absmax = [&peak](const uint4& v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = pair_to_float2<T>(w[i]);
+      peak = fmaxf(peak, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  };
+#pragma unroll
+  for (int h = 0; h < kQuantHeld; ++h) {
+    const int v = threadIdx.x + h * 256;
+    held[h] = v < vecs ? __ldg(row + v) : make_uint4(0u, 0u, 0u, 0u);
+    absmax(held[h]);
+  }
+  for (int v = threadIdx.x + kQuantHeld * 256; v < vecs; v += 256) absmax(__ldg(row + v));
+  for (int o = 16; o > 0; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+  __shared__ float warp_peak[8];
+  if ((threadIdx.x & 31) == 0) warp_peak[threadIdx.x >> 5] = peak;
+  __syncthreads();
+  peak = warp_peak[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) peak = fmaxf(peak, warp_peak[w]);
+  const float scale = fmaxf(peak, 1e-8f) * (1.0f / 127.0f);   // tensor / scalar on the reference's device
+  if (threadIdx.x == 0) scales[m] = scale;
+  uint2* out = reinterpret_cast<uint2*>(q + static_cast<int64_t>(m) * ldq);
+  auto emit = [&](int v, const uint4& in) {
+    const float2 a = pair_to_float2<T>(in.x), b = pair_to_float2<T>(in.y);
+    const float2 c = pair_to_float2<T>(in.z), d = pair_to_float2<T>(in.w);
+    out[v] = make_uint2(quantise4(a.x, a.y, b.x, b.y, scale), quantise4(c.x, c.y, d.x, d.y, scale));
+  };
+#pragma unroll
+  for (int h = 0; h < kQuantHeld; ++h) {
+    const int v = threadIdx.x + h * 256;
+    if (v < vecs) emit(v, held[h]);
+  }
+  for (int v = threadIdx.x + kQuantHeld * 256; v < vecs; v += 256) emit(v, __ldg(row + v));
+}
+
+template <typename T>
+static void launch_quantize_rows_16bit(const void* x, int64_t ldx, int M, int K, int8_t* q, int64_t ldq, float* scales,
+                                       cudaStream_t stream) {
+  const bool vec = K % 8 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && ldq % 8 == 0 &&
+                   reinterpret_cast<uintptr_t>(q) % 8 == 0;
+  if (vec)
+    quantize_rows_int8_vec_kernel<T><<<M, 256, 0, stream>>>(static_cast<const T*>(x), ldx, K, q, ldq, scales);
+  else
+    quantize_rows_int8_kernel<T><<<M, 256, 0, stream>>>(static_cast<const T*>(x), ldx, K, q, ldq, scales);
+}
+
 int launch_quantize_rows_int8(const void* x, int64_t ldx, int act_dtype, int M, int K, int8_t* q, int64_t ldq,
                               float* scales, cudaStream_t stream) {
   if (act_dtype == B200Q_F16)
-    quantize_rows_int8_kernel<__half><<<M, 256, 0, stream>>>(static_cast<const __half*>(x), ldx, K, q, ldq, scales);
+    launch_quantize_rows_16bit<__half>(x, ldx, M, K, q, ldq, scales, stream);
   else if (act_dtype == B200Q_BF16)
-    quantize_rows_int8_kernel<__nv_bfloat16><<<M, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ldx, K, q,
-                                                                   ldq, scales);
+    launch_quantize_rows_16bit<__nv_bfloat16>(x, ldx, M, K, q, ldq, scales, stream);
   else if (act_dtype == B200Q_F32)
     quantize_rows_int8_kernel<float><<<M, 256, 0, stream>>>(static_cast<const float*>(x), ldx, K, q, ldq, scales);
   else

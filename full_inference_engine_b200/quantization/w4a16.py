@@ -76,7 +76,27 @@ class W4A16Linear(nn.Module):
     # The reference sends M >= dense_threshold through a dequantised tile; here the value
     # only documents where the CUDA-core kernel hands over to the tensor-core kernel.
     dense_slab_bytes: int = 32 << 20       # reference-mode slab size (fp16 bytes at once)
-    dense_scratch_bytes: int = 8 << 20     # the per-device kernel workspace, for KV sizing
+    workspace_rows: int = 4096             # largest token count `dense_scratch_bytes` is sized for
+
+    @property
+    def dense_scratch_bytes(self) -> int:
+        """Device scratch this module's forward needs, for engines that size their KV pool from
+        it (the reference reads the attribute in ``_auto_kv_reserve``,
+        engine/continuous_batching.py:823-828): the kernel workspace for up to
+        ``workspace_rows`` tokens, in the 8 MiB granules the per-device workspace grows by.
+        Assigning the attribute overrides the figure.  ``reserve_workspace(model)`` allocates it."""
+        override = self.__dict__.get("_dense_scratch_override")
+        if override is not None:
+            return int(override)
+        try:
+            need = _lib.max_workspace_bytes(4, self.workspace_rows, self.out_features, self.in_features)
+        except (OSError, RuntimeError):
+            need = 0                       # the library is not built here: the floor below
+        return max(_lib.WORKSPACE_GRANULE, -(-need // _lib.WORKSPACE_GRANULE) * _lib.WORKSPACE_GRANULE)
+
+    @dense_scratch_bytes.setter
+    def dense_scratch_bytes(self, value: int) -> None:
+        self.__dict__["_dense_scratch_override"] = int(value)
 
     def __init__(self, in_features: int, out_features: int, *, group_size: int = GROUP_SIZE,
                  bias: bool = False, device=None):
@@ -363,6 +383,26 @@ def _download(model_name: str, revision: str | None) -> str:
 
 
 # --------------------------------------------------------------------------- reference mode, reporting
+def reserve_workspace(model: nn.Module, max_rows: int | None = None) -> int:
+    """Allocate, once, the per-device kernel workspace that every quantized projection of
+    ``model`` needs for up to ``max_rows`` tokens, and return its size in bytes.
+
+    Call it after install and BEFORE an engine hands the remaining device memory to its KV
+    pool: the workspace otherwise grows on the first forward that needs more (and cannot grow
+    during CUDA-graph capture).  No counterpart in the reference, whose scratch is the
+    dequantised tile ``dense_scratch`` grows on demand (engine/quantization/w4a16.py:62-76)."""
+    need, device = 0, None
+    for module in w4a16_modules(model):
+        if module.packed.device.type != "cuda":
+            continue
+        rows = module.workspace_rows if max_rows is None else max_rows
+        need = max(need, _lib.max_workspace_bytes(4, rows, module.out_features, module.in_features))
+        device = module.packed.device
+    if device is None:
+        return 0
+    return int(_lib.workspace_for(device, need).numel())
+
+
 def w4a16_modules(model: nn.Module) -> list[W4A16Linear]:
     return [m for m in model.modules() if isinstance(m, W4A16Linear)]
 

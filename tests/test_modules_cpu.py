@@ -182,3 +182,17 @@ def test_recursive_int8_replacement_and_storage_accounting():
     tied = nn.ModuleList([nn.Linear(8, 8), nn.Linear(8, 8)])
     tied[1].weight = tied[0].weight
     assert model_storage_bytes(tied) == 8 * 8 * 4 + 2 * 8 * 4
+
+
+def test_dense_scratch_bytes_covers_the_kernel_workspace_of_every_token_count():
+    """Engines size their KV pool from this attribute (engine/continuous_batching.py:823-828):
+    it must cover the deepest split-K workspace, which is not at the largest token count."""
+    from full_inference_engine_b200 import _lib
+
+    module = W4A16Linear(12288, 4096)
+    worst = max(_lib.workspace_bytes(4, m, 4096, 12288) for m in (1, 16, 64, 256, 1024, 4096))
+    assert module.dense_scratch_bytes >= worst
+    assert module.dense_scratch_bytes % _lib.WORKSPACE_GRANULE == 0
+    module.dense_scratch_bytes = 1 << 20            # the reference lets callers assign it
+    assert module.dense_scratch_bytes == 1 << 20
+    assert W4A16Linear(12288, 4096).dense_scratch_bytes >= worst
