@@ -20,9 +20,9 @@
 //   warp 0     TMA producer: per K block one [128 x 128 B] box of weights and one [TOK x 128 B]
 //              box of quantised activations into one ring stage
 //   warp 1     TMEM allocation, tcgen05.mma issue (four K = 32 MMAs per block), commits
-//   warps 2-5  epilogue: tcgen05.ld of the int32 accumulators, the two scales, 32-token chunks
-//              staged in shared memory and written by TMA (direct stores when y is not
-//              16-byte aligned)
+//   warps 2-9  epilogue, two groups of four warps that take alternate 32-token chunks of a tile:
+//              tcgen05.ld of the int32 accumulators, the two scales, the chunk staged in shared
+//              memory and written by TMA (direct stores when y is not 16-byte aligned)
 // Consecutive tiles share a weight tile (token tiles vary fastest), so the blocks running at
 // one time read a handful of weight tiles and all the token tiles: both stay in L2.
 #include <algorithm>
@@ -33,15 +33,18 @@
 
 namespace b200q {
 
-constexpr int kI8Threads = 32 * 6;
-constexpr int kI8EpilogueThreads = 32 * 4;
+constexpr int kI8EpilogueGroups = 2;
+constexpr int kI8GroupThreads = 32 * 4;                  // one warp per TMEM lane quarter
+constexpr int kI8EpilogueThreads = kI8EpilogueGroups * kI8GroupThreads;
+constexpr int kI8Threads = 64 + kI8EpilogueThreads;
 constexpr int kI8MaxStages = 8;
 constexpr int kI8ChunkTokens = 32;                       // tokens per staged store
 constexpr int kI8ChunkBytes = kI8ChunkTokens * kBlockN * 2;
 constexpr int kI8MaxTok = 256;
-constexpr size_t kI8SmemBudget = 226 * 1024;
-// after the ring: two staging chunks, the tile's activation scales, barriers
-constexpr size_t kI8FixedBytes = 2 * kI8ChunkBytes + kI8MaxTok * 4 + 8 * (2 * kI8MaxStages + 4) + 16;
+constexpr size_t kI8SmemBudget = 227 * 1024;             // the per-block maximum (the kernel has no static variables)
+// after the ring: two staging chunks per epilogue group, the tile's activation scales, barriers
+constexpr size_t kI8FixedBytes =
+    2 * kI8EpilogueGroups * kI8ChunkBytes + kI8MaxTok * 4 + 8 * (2 * kI8MaxStages + 4) + 16;
 
 struct I8Params {
   const float* a_scales;     // [M]
@@ -81,8 +84,11 @@ __device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
-__device__ __forceinline__ void epilogue_barrier() {
+__device__ __forceinline__ void epilogue_barrier() {           // every epilogue warp
   asm volatile("bar.sync 1, %0;" ::"n"(kI8EpilogueThreads) : "memory");
+}
+__device__ __forceinline__ void group_barrier(int group) {     // the four warps of one group
+  asm volatile("bar.sync %0, %1;" ::"r"(2 + group), "n"(kI8GroupThreads) : "memory");
 }
 
 template <typename T>
@@ -95,7 +101,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   const int stage_bytes = kWBytes + p.tok * 128;         // + [tok x 128 int8]
   const uint32_t ring = smem_base;
   const uint32_t staging = ring + p.stages * stage_bytes;
-  const uint32_t scale_buf = staging + 2 * kI8ChunkBytes;
+  const uint32_t scale_buf = staging + 2 * kI8EpilogueGroups * kI8ChunkBytes;
   const uint32_t full = scale_buf + kI8MaxTok * 4;
   const uint32_t empty = full + 8 * kI8MaxStages;
   const uint32_t acc_full = empty + 8 * kI8MaxStages;    // two
@@ -106,8 +112,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(generic_base + (tmem_slot - smem_base));
   volatile int* abort_p = reinterpret_cast<volatile int*>(generic_base + (abort_slot - smem_base));
   float* const scale_p = reinterpret_cast<float*>(generic_base + (scale_buf - smem_base));
-  __shared__ unsigned local_status;
-  unsigned* status = p.status != nullptr ? p.status : &local_status;
+  // without a workspace the status word is a private one that nobody reads
+  unsigned* const local_status = reinterpret_cast<unsigned*>(generic_base + (abort_slot + 4 - smem_base));
+  unsigned* status = p.status != nullptr ? p.status : local_status;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -126,7 +133,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     }
     if (lane == 0) {
       *abort_p = 0;
-      local_status = 0u;
+      *local_status = 0u;
       tma_prefetch_desc(&tm_w);
       tma_prefetch_desc(&tm_x);
       if (p.tma_out) tma_prefetch_desc(&tm_y);
@@ -200,11 +207,13 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       if (!ok) flag_failure(abort_p, status, 2u);
     }
   } else {
-    // warps 2..5 read TMEM lane quarters 2, 3, 0, 1 (a warp may only touch quarter warp % 4)
+    // a warp may only touch TMEM lane quarter warp % 4; the group is the other index
     const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
     const int ch = quarter * 32 + lane;
     const int et = static_cast<int>(threadIdx.x) - (kI8Threads - kI8EpilogueThreads);
-    const bool issuer = et == 0;
+    const bool issuer = (et & (kI8GroupThreads - 1)) == 0;       // one thread per group issues its stores
+    const uint32_t my_staging = staging + static_cast<uint32_t>(group) * 2 * kI8ChunkBytes;
     T* const y = static_cast<T*>(p.y);
     int chunk_no = 0;
     for (int i = 0; i < my_tiles; ++i) {
@@ -227,7 +236,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       tc_fence_after_sync();
       const uint32_t acc_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(b * p.acc_cols);
       const int tok_here = min(p.tok, (p.M - m_base + kI8ChunkTokens - 1) / kI8ChunkTokens * kI8ChunkTokens);
-      for (int c = 0; c < tok_here; c += kI8ChunkTokens, ++chunk_no) {
+      const int stride = kI8EpilogueGroups * kI8ChunkTokens;
+      bool released = false;
+      for (int c = group * kI8ChunkTokens; c < tok_here; c += stride, ++chunk_no) {
         uint32_t r[kI8ChunkTokens];
 #pragma unroll
         for (int j = 0; j < kI8ChunkTokens; ++j) r[j] = 0u;
@@ -237,16 +248,17 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             tmem_ld_x8(acc_addr + c + 8 * q, *reinterpret_cast<uint32_t(*)[8]>(&r[8 * q]));
           tmem_ld_wait();
         }
-        if (c + kI8ChunkTokens >= tok_here) {
-          // the accumulator is in registers: hand it back to the MMA warp
+        if (c + stride >= tok_here) {
+          // this group's share of the accumulator is in registers: hand it back to the MMA warp
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty + 8 * b);
+          released = true;
         }
         if (p.tma_out) {
-          const uint32_t buf = staging + static_cast<uint32_t>(chunk_no & 1) * kI8ChunkBytes;
+          const uint32_t buf = my_staging + static_cast<uint32_t>(chunk_no & 1) * kI8ChunkBytes;
           if (issuer) tma_store_wait_read<1>();            // the store that last used this buffer has read it
-          epilogue_barrier();
+          group_barrier(group);
 #pragma unroll
           for (int j = 0; j < kI8ChunkTokens; j += 2) {
             // the reference's order: (float(acc) * activation scale) * weight scale, one rounding to T
@@ -258,7 +270,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                          : "memory");
           }
           fence_proxy_async_smem();                        // staged rows -> visible to the TMA engine
-          epilogue_barrier();
+          group_barrier(group);
           if (issuer && ok) {
             tma_store_3d(&tm_y, buf, n_tile * kBlockN, m_base + c, 0);   // rows >= M and channels >= N are clipped
             tma_store_commit();
@@ -272,6 +284,12 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                   from_float<T>((static_cast<float>(static_cast<int>(r[j])) * scale_p[c + j]) * w_scale);
           }
         }
+      }
+      if (!released) {
+        // a short last tile left this group without a chunk: it still owes its arrivals
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + 8 * b);
       }
     }
     if (issuer) tma_store_wait_all();
