@@ -397,12 +397,56 @@ __global__ void __launch_bounds__(256) quantize_rows_int8_vec_kernel(const T* __
   for (int v = threadIdx.x + kQuantHeld * 256; v < vecs; v += 256) emit(v, __ldg(row + v));
 }
 
+// Short rows (at most 32 x 8 x kQuantWarpHeld values): one WARP per row, eight rows per block, the
+// whole row in registers, no block barrier.
+constexpr int kQuantWarpHeld = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_rows_int8_warp_kernel(const T* __restrict__ x, int64_t ldx, int M, int K,
+                                                                      int8_t* __restrict__ q, int64_t ldq,
+                                                                      float* __restrict__ scales) {
+  const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (m >= M) return;
+  const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * ldx);
+  const int vecs = K / 8;
+  uint4 held[kQuantWarpHeld];
+  float peak = 0.0f;
+#pragma unroll
+  for (int h = 0; h < kQuantWarpHeld; ++h) {
+    const int v = lane + h * 32;
+    held[h] = v < vecs ? __ldg(row + v) : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t w[4] = {held[h].x, held[h].y, held[h].z, held[h].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = pair_to_float2<T>(w[i]);
+      peak = fmaxf(peak, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+  const float scale = fmaxf(peak, 1e-8f) * (1.0f / 127.0f);   // tensor / scalar on the reference's device
+  if (lane == 0) scales[m] = scale;
+  uint2* out = reinterpret_cast<uint2*>(q + static_cast<int64_t>(m) * ldq);
+#pragma unroll
+  for (int h = 0; h < kQuantWarpHeld; ++h) {
+    const int v = lane + h * 32;
+    if (v < vecs) {
+      const float2 a = pair_to_float2<T>(held[h].x), b = pair_to_float2<T>(held[h].y);
+      const float2 c = pair_to_float2<T>(held[h].z), d = pair_to_float2<T>(held[h].w);
+      out[v] = make_uint2(quantise4(a.x, a.y, b.x, b.y, scale), quantise4(c.x, c.y, d.x, d.y, scale));
+    }
+  }
+}
+
 template <typename T>
 static void launch_quantize_rows_16bit(const void* x, int64_t ldx, int M, int K, int8_t* q, int64_t ldq, float* scales,
                                        cudaStream_t stream) {
   const bool vec = K % 8 == 0 && ldx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && ldq % 8 == 0 &&
                    reinterpret_cast<uintptr_t>(q) % 8 == 0;
-  if (vec)
+  if (vec && K <= 32 * 8 * kQuantWarpHeld && M >= 64)
+    quantize_rows_int8_warp_kernel<T><<<(M + 7) / 8, 256, 0, stream>>>(static_cast<const T*>(x), ldx, M, K, q, ldq,
+                                                                      scales);
+  else if (vec)
     quantize_rows_int8_vec_kernel<T><<<M, 256, 0, stream>>>(static_cast<const T*>(x), ldx, K, q, ldq, scales);
   else
     quantize_rows_int8_kernel<T><<<M, 256, 0, stream>>>(static_cast<const T*>(x), ldx, K, q, ldq, scales);

@@ -50,7 +50,7 @@ namespace b200q {
 constexpr int kSkGroups = 2;                                   // dequantise groups
 constexpr int kSkThreads = 32 * (2 + 4 + 4 * kSkGroups);       // 448
 constexpr int kSkMaxStages = 16;                               // weight ring
-constexpr int kSkXStages = 4;                                  // activation ring
+constexpr int kSkXStages = 4;                                  // activation ring (most; wide token tiles take two)
 constexpr int kSkSStages = 3;                                  // scale-chunk ring (4-bit formats)
 constexpr int kSkAStages = 3;                                  // operand stages in tensor memory
 constexpr int kSkMaxTok = 64;
@@ -78,6 +78,7 @@ struct SkParams {
   int kb_total;          // K / 128
   uint32_t total_units;  // weight tiles x K blocks
   int stages;            // weight ring depth
+  int x_stages;          // activation ring depth
   uint32_t idesc;
   int static_weights;
   int swiglu;
@@ -151,7 +152,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   const int x_bytes = 2 * x_atom_bytes;
   const int S = p.stages;
   const uint32_t x_ring = smem_base;                               // 1024-byte aligned atoms
-  const uint32_t w_ring = x_ring + kSkXStages * x_bytes;
+  const uint32_t w_ring = x_ring + p.x_stages * x_bytes;
   const uint32_t s_ring = w_ring + S * kWBytes;
   const uint32_t bars = s_ring + kSkSStages * kSBytes;
   const uint32_t w_full = bars;                                    // [kSkMaxStages]
@@ -287,7 +288,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tma_load_3d(x_ring + sx * x_bytes, &tm_x, x_full + 8 * sx, 0, 0, 2 * x_kb);
           ++ix;
           if (++x_kb == KB) x_kb = 0;
-          if (++sx == kSkXStages) {
+          if (++sx == p.x_stages) {
             sx = 0;
             px ^= 1;
           }
@@ -309,7 +310,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if (*abort_p) {
         // let the copies already in flight land before the block's shared memory is released
         for (int j = max(0, iw - S); j < iw; ++j) mbar_wait(w_full + 8 * (j % S), (j / S) & 1);
-        for (int j = max(0, ix - kSkXStages); j < ix; ++j) mbar_wait(x_full + 8 * (j % kSkXStages), (j / kSkXStages) & 1);
+        for (int j = max(0, ix - p.x_stages); j < ix; ++j) mbar_wait(x_full + 8 * (j % p.x_stages), (j / p.x_stages) & 1);
         for (int j = max(0, ic - kSkSStages); j < ic; ++j) mbar_wait(s_full + 8 * (j % kSkSStages), (j / kSkSStages) & 1);
       }
     }
@@ -348,7 +349,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         if (seg_last) umma_commit(acc_full);
         seg_first = seg_last;
         if (++kb == KB) kb = 0;
-        if (++sx == kSkXStages) {
+        if (++sx == p.x_stages) {
           sx = 0;
           x_phase ^= 1;
         }
@@ -696,7 +697,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 
 // ---------------------------------------------------------------- host side
 struct SkPlan {
-  int tok, n_tiles, kb_total, stages, grid;
+  int tok, n_tiles, kb_total, stages, x_stages, grid;
   uint32_t units;
   size_t smem_bytes;
 };
@@ -737,7 +738,10 @@ static SkPlan sk_plan(int format, int M, int N, int K, int sms) {
   // the next kernel's block fits beside this one), otherwise the whole SM.
   const size_t w_stage = format == FMT_W8 ? kBlockN * 128 : kBlockN * 64;
   const size_t chunk = format == FMT_W8 ? 0 : static_cast<size_t>(kSkChunkBytes) * (format == FMT_W4_ASYM ? 2 : 1);
-  const size_t fixed = 1024 + kSkBarrierBytes + static_cast<size_t>(kSkXStages) * pl.tok * 256 + kSkSStages * chunk;
+  // wide token tiles keep two activation stages (16 KB each at 64 rows; the collecting owner
+  // needs rows x 512 bytes of the ring as its summing buffer), so that the block still fits half an SM
+  pl.x_stages = pl.tok > 32 ? 2 : kSkXStages;
+  const size_t fixed = 1024 + kSkBarrierBytes + static_cast<size_t>(pl.x_stages) * pl.tok * 256 + kSkSStages * chunk;
   int stages = kSkHalfSm > fixed ? static_cast<int>((kSkHalfSm - fixed) / w_stage) : 0;
   if (stages < 6) stages = static_cast<int>((kSkFullSm - fixed) / w_stage);
   pl.stages = std::max(2, std::min(stages, kSkMaxStages));
@@ -849,6 +853,7 @@ static int launch_sk_typed(const ForwardArgs& a, const SkPlan& pl) {
   p.kb_total = pl.kb_total;
   p.total_units = pl.units;
   p.stages = pl.stages;
+  p.x_stages = pl.x_stages;
   const uint32_t ab_fmt = a.act_dtype == B200Q_F16 ? 0u : 1u;    // both operands in the activation dtype
   p.idesc = umma_idesc_f16(ab_fmt, ab_fmt, 128u, static_cast<uint32_t>(pl.tok));
   p.static_weights = a.static_weights ? 1 : 0;
