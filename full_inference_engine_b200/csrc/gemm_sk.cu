@@ -551,9 +551,11 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------ dequantise groups
-    // Every warp walks every unit (cheap bookkeeping) and unpacks those of its group; every
-    // warp also takes every scale chunk in order (its row's eight scales into registers), so a
-    // chunk slot is released by exactly eight arrivals.
+    // A warp visits only the units of its group (ring positions advance by the group count: the
+    // bookkeeping of a skipped unit cost as much issue time as it saved); every warp still
+    // takes every scale chunk in order (its row's eight scales into registers), so a chunk slot
+    // is released by exactly eight arrivals.  Unit j lies in chunk ((kbi0 + j) >> 3) - (kbi0 >> 3):
+    // a tile's K blocks are a multiple of eight, so chunks never straddle tiles.
     const int g = (warp - 6) >> 2;                          // group: units g, g + 2, ...
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                    // channel inside the tile = TMEM lane
@@ -561,22 +563,30 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const int xr = (row >> 1) & 3;                          // 64-byte swizzle term of this row
     uint4 cs = make_uint4(0u, 0u, 0u, 0u), cz = make_uint4(0u, 0u, 0u, 0u);   // the current chunk
     bool ok = true;
-    int kb = kbi0, sw = 0, as = 0, sc = 0;
+    // positions of this group's first unit (the rings are at least two deep, the operand stages three)
+    int kb = kbi0 + g, sw = g, as = g, sc = 0;
+    while (kb >= KB) kb -= KB;
     uint32_t w_phase = 0, ae_phase = 1, c_phase = 0;
-    for (int j = 0; j < n_units && ok; ++j) {
-      if (kGroups && (j == 0 || (kb & 7) == 0)) {
-        ok = wait_or_abort(s_full + 8 * sc, c_phase, abort_p);
-        if (!ok) break;
-        cs = ld_shared_v4(s_ring + sc * kSBytes + row * 16);
-        if (FMT == FMT_W4_ASYM) cz = ld_shared_v4(s_ring + sc * kSBytes + kSkChunkBytes + row * 16);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_empty + 8 * sc);
-        if (++sc == kSkSStages) {
-          sc = 0;
-          c_phase ^= 1;
+    int chunks_taken = 0;                                   // scale chunks this warp has consumed
+    for (int j = g; j < n_units && ok; j += kSkGroups) {
+      if (kGroups) {
+        const int chunk = ((kbi0 + j) >> 3) - (kbi0 >> 3);
+        while (chunks_taken <= chunk) {                     // at most two steps: a group moves two units at a time
+          ok = wait_or_abort(s_full + 8 * sc, c_phase, abort_p);
+          if (!ok) break;
+          cs = ld_shared_v4(s_ring + sc * kSBytes + row * 16);
+          if (FMT == FMT_W4_ASYM) cz = ld_shared_v4(s_ring + sc * kSBytes + kSkChunkBytes + row * 16);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty + 8 * sc);
+          if (++sc == kSkSStages) {
+            sc = 0;
+            c_phase ^= 1;
+          }
+          ++chunks_taken;
         }
+        if (!ok) break;
       }
-      if ((j & (kSkGroups - 1)) == g) {
+      {
         PairConsts gp{0u, 0u, 0u};
         if (kGroups)
           gp = make_pair_consts(pick_half(cs, kb & 7),
@@ -674,13 +684,16 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           mbar_arrive(w_empty + 8 * sw);
         }
       }
-      if (++kb == KB) kb = 0;
-      if (++sw == S) {
-        sw = 0;
+      kb += kSkGroups;
+      while (kb >= KB) kb -= KB;                          // (a one-block K wraps twice)
+      sw += kSkGroups;
+      if (sw >= S) {
+        sw -= S;
         w_phase ^= 1;
       }
-      if (++as == kSkAStages) {
-        as = 0;
+      as += kSkGroups;
+      if (as >= kSkAStages) {
+        as -= kSkAStages;
         ae_phase ^= 1;
       }
     }
