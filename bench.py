@@ -492,8 +492,11 @@ def config_dict(args, cases):
         + ("W8: int8 per-channel, fp16 scale" if any(c.fmt == "w8" for c in cases) else ""),
         "cases": len(cases),
         "parallelism": (f"N-sharded x{args.gpus}, all-gather "
-                        + ("fused into the kernel epilogue (peer stores over NVLink)"
-                           if args.gather == "fused" else "by NCCL")) if args.gpus > 1 else "single GPU",
+                        + {"fused": "by this library's own kernels (peer stores over NVLink, no NCCL): from the "
+                                    "GEMM kernel's epilogue, or by a push kernel where a rank has few large tiles",
+                           "epilogue": "fused into the GEMM kernel's epilogue (peer stores over NVLink)",
+                           "push": "by this library's push kernel after the GEMM (peer stores over NVLink)",
+                           "nccl": "by NCCL"}[args.gather]) if args.gpus > 1 else "single GPU",
         "l2": "inputs larger than L2: every launch reads its own weight buffer and step variants "
               "alternate, so that at least 2 x 126 MiB of distinct weights pass between two uses of a buffer",
     }
@@ -569,15 +572,16 @@ def run_b200(args, cases):
 
     def forward_gather(i, case, x, w, how):
         """This rank's columns of case i delivered to every rank; returns the full [M, N] view."""
-        if how == "fused":
+        if how in ("fused", "epilogue", "push"):
             from full_inference_engine_b200.quantization.sharded import fused_forward_gather
 
+            form = "auto" if how == "fused" else how
             if case.fmt == "w8":
-                ok = fused_forward_gather(x, fused_out[i], qweight=w[0], scales=w[1])
+                ok = fused_forward_gather(x, fused_out[i], qweight=w[0], scales=w[1], form=form)
             elif case.fmt == "w4_ref":
-                ok = fused_forward_gather(x, fused_out[i], packed=w[0], scales=w[1])
+                ok = fused_forward_gather(x, fused_out[i], packed=w[0], scales=w[1], form=form)
             else:
-                ok = fused_forward_gather(x, fused_out[i], packed=w[0], scales=w[1], zeros=w[2])
+                ok = fused_forward_gather(x, fused_out[i], packed=w[0], scales=w[1], zeros=w[2], form=form)
             if ok:
                 return fused_out[i].tensor
         y = forward(case, x, w)
@@ -585,7 +589,9 @@ def run_b200(args, cases):
         return gathered[i].permute(1, 0, 2).reshape(case.m, -1)
 
     def one_step(variant: int, how: str):
-        """how: "local" (this rank's GEMMs only), "fused" or "nccl" (GEMM + all-gather)."""
+        """how: "local" (this rank's GEMMs only); GEMM + all-gather: "fused" (this library's own
+        exchange over peer memory, form picked per geometry), "epilogue" (always from the GEMM's
+        epilogue), "push" (always forward + push kernel) or "nccl"."""
         outs = []
         for i, case in enumerate(local_cases):
             w = weights_of(i, variant)
@@ -609,7 +615,7 @@ def run_b200(args, cases):
     gather_parity = None
     if world > 1:
         worst, bad = 0.0, []
-        for how in ("fused", "nccl"):
+        for how in ("fused", "epilogue", "push", "nccl"):
             for i, case in enumerate(local_cases):
                 got = forward_gather(i, case, acts[i], weights_of(i, 0), how).float()
                 want = forward(cases[i], acts[i], full_sets[cases[i].wkey]).float()
@@ -621,7 +627,7 @@ def run_b200(args, cases):
         flag = torch.tensor([worst, float(len(bad))], dtype=torch.float64)
         dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=cpu_group)
         gather_parity = {"max_rel_err": float(flag[0]), "ok": float(flag[1]) == 0.0,
-                         "cases": 2 * len(cases), "bar": 1e-2,
+                         "cases": 4 * len(cases), "bar": 1e-2,
                          "against": "this rank's single-GPU forward of the whole matrix",
                          "failed_on_rank0": bad}
         del full_sets
@@ -762,7 +768,7 @@ def run_b200(args, cases):
     phase_ms = {}
     if world > 1:
         phase_ms[args.gather] = ms_step
-        for how in ("local", "fused", "nccl"):
+        for how in ("local", "fused", "epilogue", "push", "nccl"):
             if how in phase_ms:
                 continue
             torch.cuda.synchronize()
@@ -806,7 +812,7 @@ def run_b200(args, cases):
         reps = len(sets)
         entry = {"case": cases[i].key, "config": case.cfg, "M": case.m, "K": case.k, "N": cases[i].n,
                  "dtype": "fp16" if case.dtype is torch.float16 else "bf16", "kernel": kernel_of(case)}
-        hows = ("local",) if world == 1 else ("local", "fused", "nccl")
+        hows = ("local",) if world == 1 else ("local", "fused", "epilogue", "push", "nccl")
         for how in hows:
             def launch(w, how=how):
                 if how == "local":
@@ -955,10 +961,12 @@ def run_b200(args, cases):
             "phases": None if world == 1 else {
                 "sharded_gemm_only_ms_per_step": round(phase_ms["local"], 5) if "local" in phase_ms else None,
                 "with_fused_all_gather_ms_per_step": round(phase_ms["fused"], 5) if "fused" in phase_ms else None,
+                "with_epilogue_all_gather_ms_per_step": round(phase_ms["epilogue"], 5) if "epilogue" in phase_ms else None,
+                "with_push_all_gather_ms_per_step": round(phase_ms["push"], 5) if "push" in phase_ms else None,
                 "with_nccl_all_gather_ms_per_step": round(phase_ms["nccl"], 5) if "nccl" in phase_ms else None,
                 "timed_value_is": args.gather,
-                "per_case": "per_case[*].us is the sharded GEMM alone, fused_gather_us / nccl_gather_us "
-                            "the GEMM with that all-gather"},
+                "per_case": "per_case[*].us is the sharded GEMM alone, fused_gather_us / epilogue_gather_us / "
+                            "push_gather_us / nccl_gather_us the GEMM with that all-gather"},
             "gather_parity": gather_parity,
             "ffn_pairing": ffn_pairing,
             "device_status": status,
@@ -1200,7 +1208,7 @@ def main():
     ap.add_argument("--workload", default="all", choices=["all", "c1", "c2", "c3", "c3fused", "c4", "c5", "mlp", "head", "w8a8"])
     ap.add_argument("--layout", default="asym", choices=["asym", "ref"])
     ap.add_argument("--cases", default="", help="comma list of substrings; keep only matching case keys")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--gather", default="fused", choices=["fused", "epilogue", "push", "nccl"],
                     help="at --gpus > 1: the all-gather that `value` times (both are reported in `phases`)")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--profile", action="store_true",

@@ -23,6 +23,8 @@ KERNEL_AUTO, KERNEL_SIMT, KERNEL_TC, KERNEL_STREAMK = 0, 1, 2, 3
 FLAG_STATIC_WEIGHTS = 0x100
 FLAG_SWIGLU_PAIRS = 0x200
 FLAG_ARGMAX = 0x400
+FLAG_GATHER_EPILOGUE = 0x800
+FLAG_GATHER_PUSH = 0x1000
 W8_SCALE_F16, W8_SCALE_F32 = 0, 1
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_WAIT = range(7)
 

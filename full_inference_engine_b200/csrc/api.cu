@@ -64,6 +64,36 @@ static int run_forward(ForwardArgs& a, int kernel_and_flags) {
   return launch_forward_tc(a);
 }
 
+// Two ways to deliver a column-parallel forward's output to the peers.  The epilogue form (every
+// block of the forward stores its tile into every rank's buffer) hides the peer stores behind
+// other blocks' compute, but a single SM sustains only a few GB/s of them: with few, large tiles
+// the stores of (world - 1) x tile bytes per block dominate.  The push form (a plain forward into
+// this rank's own buffer — every kernel and routing rule available — then a kernel that copies
+// the slab to the peers from hundreds of blocks) costs about 6 us more in fixed latency.
+// Measured on 2 and 4 GPUs (B200, NVLink): push wins at M = 256..512 with N_local <= 3072
+// (28 against 34 us, 34 against 41 us) and for the single-row int8 GEMV, the epilogue everywhere
+// else.  B200Q_FLAG_GATHER_EPILOGUE / B200Q_FLAG_GATHER_PUSH force one form.
+static bool gather_by_push(const ForwardArgs& a, const b200q_gather* g, int flags) {
+  if (g->world < 2 || a.N % 8 || a.ldy % 8) return false;       // the push moves whole 16-byte chunks
+  for (int r = 0; r < g->world; ++r)
+    if (reinterpret_cast<uintptr_t>(g->y_peer[r]) % 16) return false;
+  if (flags & B200Q_FLAG_GATHER_EPILOGUE) return false;
+  if (flags & B200Q_FLAG_GATHER_PUSH) return true;
+  if (a.format == FMT_W8 && a.M <= kSimtMaxRowsW8) return true;  // the CUDA-core kernel has no gather epilogue
+  const int tiles = tc_output_tiles(a.format, a.M, a.N, a.K);
+  const long long per_block = static_cast<long long>(tc_tile_bytes(a.format, a.M, a.N, a.K)) * (g->world - 1);
+  return tiles > 0 && tiles <= 32 && per_block >= 96 * 1024;
+}
+
+static int forward_then_push(ForwardArgs& a, const b200q_gather* g, int tiles, int flags) {
+  if (tiles <= 0) return B200Q_ERR_UNSUPPORTED;
+  a.gather = nullptr;
+  a.announce = g;
+  a.y = static_cast<unsigned char*>(g->y_peer[g->rank]) + static_cast<size_t>(g->rank) * a.N * 2;
+  if (int st = run_forward(a, B200Q_KERNEL_AUTO | (flags & B200Q_FLAG_STATIC_WEIGHTS))) return st;
+  return launch_gather_push(g, a.ldy, a.M, a.N, tiles, a.stream);
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -280,6 +310,8 @@ int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   a.gather = gather;
   a.static_weights = (flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
   a.stream = static_cast<cudaStream_t>(stream);
+  if (gather_by_push(a, gather, flags))
+    return forward_then_push(a, gather, b200q_gather_tiles(4, M, N_local, K, group), flags);
   return launch_forward_tc(a);
 }
 
@@ -304,6 +336,8 @@ int b200q_w8a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const 
   a.gather = gather;
   a.static_weights = (flags & B200Q_FLAG_STATIC_WEIGHTS) != 0;
   a.stream = static_cast<cudaStream_t>(stream);
+  if (gather_by_push(a, gather, flags))
+    return forward_then_push(a, gather, b200q_gather_tiles(8, M, N_local, K, 0), flags);
   return launch_forward_tc(a);
 }
 

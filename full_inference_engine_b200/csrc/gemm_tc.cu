@@ -72,6 +72,9 @@ struct TcParams {
   int g_world, g_rank, g_col0;
   void* g_y[8];
   unsigned long long* g_sig[8];   // each rank's signal block (see GatherSignal)
+  // plain forward ahead of a push kernel (a_world > 1, g_world == 0): only the "entered the
+  // call" announcement is made here, early, so that the push kernel finds the peers ready
+  int a_world, a_rank;
   // fused all-reduce of a row-parallel (K-sharded) forward (reduce != 0, g_world > 1): every
   // rank computes a partial [M, N]; the rank that owns a column block adds the other ranks'
   // partials (delivered into its inbox as self-validating fp32 words) in rank order and
@@ -124,6 +127,94 @@ __global__ void gather_wait_kernel(unsigned long long* sig, unsigned long long e
   if (!poll_at_least(sig + kSigArrivals, gen * expected)) sig[kSigStatus] = 1ull;
   sig[kSigGeneration] = gen;
   __threadfence_system();
+}
+
+// All-gather by push: after a plain forward has written this rank's [M, n_local] slab into its own
+// copy of the full output, every block copies a share of the slab into the same place of every
+// peer's copy (16-byte loads, one 16-byte peer store per destination), so the NVLink writes are
+// spread over as many SMs as the slab is worth instead of over the few blocks that own output
+// tiles.  Protocol, on the same signal block as the epilogue form: announce "entered call g"
+// to the peers, wait (bounded) for theirs before the first store into their buffers, and when
+// the LAST block of this grid has made its stores visible, count `tiles` arrivals on every rank —
+// the number gather_wait_kernel expects from a rank, whichever way the tiles travelled.
+struct PushParams {
+  unsigned char* y[8];            // peer-mapped bases of every rank's full output
+  unsigned long long* sig[8];
+  int rank, world;
+  int rows;
+  long long ld_bytes;             // row pitch of the full output
+  long long col0_bytes;           // this rank's slab starts here in every row
+  int row_chunks;                 // 16-byte chunks per slab row
+  unsigned long long tiles;
+};
+
+__global__ void __launch_bounds__(512) gather_push_kernel(const PushParams p) {
+  grid_launch_dependents();
+  grid_dependency_wait();                                   // the forward that wrote the slab
+  unsigned long long* const mine = p.sig[p.rank];
+  const unsigned long long gen = mine[kSigGeneration] + 1;
+  if (blockIdx.x == 0 && threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank)
+    st_relaxed_sys(p.sig[threadIdx.x] + kSigReady + p.rank, gen);
+  if (threadIdx.x < p.world && static_cast<int>(threadIdx.x) != p.rank) {
+    if (!poll_at_least(mine + kSigReady + threadIdx.x, gen)) mine[kSigStatus] = 2ull;
+  }
+  __syncthreads();
+  const long long total = static_cast<long long>(p.rows) * p.row_chunks;
+  const unsigned char* const src = p.y[p.rank];
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / p.row_chunks, c = i - r * p.row_chunks;
+    const long long off = r * p.ld_bytes + p.col0_bytes + c * 16;
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + off));
+#pragma unroll
+    for (int d = 0; d < 8; ++d)
+      if (d < p.world && d != p.rank) *reinterpret_cast<uint4*>(p.y[d] + off) = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();                                 // this block's peer stores are visible
+    unsigned long long* const done = mine + kSigPushBlocks;
+    if (atomicAdd(done, 1ull) == gridDim.x - 1) {
+      *done = 0ull;                                         // for the next call
+      __threadfence_system();                               // cumulative: every block's stores before the counts
+      for (int d = 0; d < p.world; ++d) red_add_relaxed_sys(p.sig[d] + kSigArrivals, p.tiles);
+    }
+  }
+}
+
+int launch_gather_push(const b200q_gather* g, int64_t ldy, int M, int n_local, int tiles, cudaStream_t stream) {
+  PushParams p{};
+  for (int r = 0; r < g->world; ++r) {
+    p.y[r] = static_cast<unsigned char*>(g->y_peer[r]);
+    p.sig[r] = static_cast<unsigned long long*>(g->signal_peer[r]);
+  }
+  p.rank = g->rank;
+  p.world = g->world;
+  p.rows = M;
+  p.ld_bytes = ldy * 2;
+  p.col0_bytes = static_cast<long long>(g->rank) * n_local * 2;
+  p.row_chunks = n_local * 2 / 16;
+  p.tiles = static_cast<unsigned long long>(tiles);
+  // one block per 4 KiB of peer stores (a single SM sustains only a few GB/s of them), at most
+  // four per SM
+  const long long out_bytes = static_cast<long long>(M) * n_local * 2 * (g->world - 1);
+  const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(592, (out_bytes + 4095) / 4096)));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(512);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gather_push_kernel, p);
+  if (e != cudaSuccess) {
+    set_last_error("cudaLaunchKernelEx(gather_push)", e);
+    return B200Q_ERR_CUDA;
+  }
+  return note_launch();
 }
 
 template <int FMT, typename T, int DW>
@@ -276,15 +367,17 @@ wq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      if (p.g_world > 1 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+      if ((p.g_world > 1 || p.a_world > 1) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
         // Fused all-gather: tell every rank that this rank has entered call `gen`, i.e. that
         // whatever read its previous output has finished (it precedes us in the stream).
         grid_dependency_wait();
-        const unsigned long long gen = p.g_sig[p.g_rank][kSigGeneration] + 1;
+        const int world = p.g_world > 1 ? p.g_world : p.a_world;
+        const int rank = p.g_world > 1 ? p.g_rank : p.a_rank;
+        const unsigned long long gen = p.g_sig[rank][kSigGeneration] + 1;
         // Relaxed: the announcement publishes no data of this kernel, only that the kernels
         // before it in the stream have finished (they have: griddepcontrol.wait returned).  A
         // release store per peer would serialise one NVLink round trip per rank.
-        for (int d = 0; d < p.g_world; ++d) st_relaxed_sys(p.g_sig[d] + kSigReady + p.g_rank, gen);
+        for (int d = 0; d < world; ++d) st_relaxed_sys(p.g_sig[d] + kSigReady + rank, gen);
       }
       bool ok = true;
       int sa = 0, sx = 0, xs = 0;                // operand stage, activation chunk slot, block in chunk
@@ -1313,6 +1406,13 @@ static int launch_tc_typed(const ForwardArgs& a, const TcPlan& pl) {
       p.g_sig[d] = d < a.gather->world ? static_cast<unsigned long long*>(a.gather->signal_peer[d]) : nullptr;
     }
   }
+  p.a_world = 0;
+  if (!gathering && !reducing && a.announce != nullptr && a.announce->world > 1) {
+    p.a_world = a.announce->world;
+    p.a_rank = a.announce->rank;
+    for (int d = 0; d < 8; ++d)
+      p.g_sig[d] = d < p.a_world ? static_cast<unsigned long long*>(a.announce->signal_peer[d]) : nullptr;
+  }
   p.reduce = 0;
   if (reducing) {
     p.reduce = 1;
@@ -1421,6 +1521,14 @@ int tc_output_tiles(int format, int M, int N, int K) {
   if (sk > 0) return sk;
   const TcPlan pl = make_plan(format, M, N, K);
   return pl.m_tiles * pl.n_tiles;
+}
+
+// Bytes of one output tile of the tile kernel's plan for this geometry (what a block of the
+// epilogue form of the all-gather stores into EACH peer).
+int tc_tile_bytes(int format, int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const TcPlan pl = make_plan(format, M, N, K);
+  return pl.tok * kBlockN * 2;
 }
 
 // One line naming the kernel instantiation and tiling a plain forward of this geometry takes.

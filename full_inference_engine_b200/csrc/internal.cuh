@@ -37,6 +37,7 @@ struct ForwardArgs {
   bool force_streamk;   // B200Q_KERNEL_STREAMK: the persistent stream-K variant or nothing
   const b200q_gather* gather;  // fused all-gather destinations, or null
   const b200q_reduce* reduce;  // fused all-reduce of a row-parallel forward, or null
+  const b200q_gather* announce;  // a push kernel follows: announce the call to these peers early, or null
   cudaStream_t stream;
 };
 
@@ -61,9 +62,11 @@ bool tc_supported(const ForwardArgs& a);
 size_t tc_workspace_bytes(int format, int M, int N, int K);
 int launch_forward_tc(const ForwardArgs& a);
 int tc_output_tiles(int format, int M, int N, int K);
+int tc_tile_bytes(int format, int M, int N, int K);
 int tc_reduce_tiles(int format, int M, int N, int K_local, int world);
 void tc_describe_plan(int format, int M, int N, int K, char* text, size_t size);
 int launch_gather_wait(const b200q_gather* g, unsigned long long expected, cudaStream_t stream);
+int launch_gather_push(const b200q_gather* g, int64_t ldy, int M, int n_local, int tiles, cudaStream_t stream);
 
 // gemm_i8.cu — W8A8: per-row activation quantisation and the int8 x int8 tensor-core GEMM.
 int launch_quantize_rows_int8(const void* x, int64_t ldx, int act_dtype, int M, int K, int8_t* q, int64_t ldq,

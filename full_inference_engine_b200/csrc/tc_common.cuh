@@ -166,8 +166,9 @@ __device__ __forceinline__ void tmem_st_cols<32>(uint32_t taddr, const uint32_t 
 //   [0]     arrivals: +1 for every unit of output a rank has delivered everywhere
 //   [1]     generation: calls completed on this rank (advanced by gather_wait_kernel)
 //   [2]     status: non-zero if a bounded wait of the protocol expired on this rank
+//   [3]     blocks of the push kernel that have finished (this rank only; zero between calls)
 //   [8 + r] ready[r]: rank r has entered call number ready[r] (so its previous output is consumed)
-constexpr int kSigArrivals = 0, kSigGeneration = 1, kSigStatus = 2, kSigReady = 8;
+constexpr int kSigArrivals = 0, kSigGeneration = 1, kSigStatus = 2, kSigPushBlocks = 3, kSigReady = 8;
 
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
   unsigned long long v;

@@ -83,9 +83,15 @@ class SymmetricOutput:
 
 
 def fused_forward_gather(rows: torch.Tensor, out: SymmetricOutput, *, qweight=None, packed=None,
-                         scales=None, zeros=None, bias=None, group_size: int = 128) -> bool:
-    """One kernel computes this rank's columns and stores them into every rank's ``out``;
-    a wait kernel then holds the stream until all ranks' columns have arrived here.
+                         scales=None, zeros=None, bias=None, group_size: int = 128,
+                         form: str = "auto") -> bool:
+    """This rank's columns reach every rank's ``out`` through this library's own kernels over
+    peer memory (no NCCL); a wait kernel then holds the stream until all ranks' columns have
+    arrived here.  ``form``: ``"epilogue"`` — every block of the forward kernel stores its
+    finished tile into every rank's buffer; ``"push"`` — a plain forward into this rank's own
+    buffer, then a kernel that copies the slab to the peers from hundreds of blocks;
+    ``"auto"`` — the library picks by geometry (few large tiles are pushed).  Every rank must
+    pass the same ``form``.
 
     Pass ``qweight`` (int8) for W8A16 or ``packed`` (uint8 reference layout, or int32 with
     ``zeros`` for the asymmetric layout) for INT4; the tensors hold this rank's rows only.
@@ -103,6 +109,11 @@ def fused_forward_gather(rows: torch.Tensor, out: SymmetricOutput, *, qweight=No
     ws = _lib.workspace_for(rows.device, _lib.workspace_bytes(4 if is_w4 else 8, m, n_local, k))
     stream = _lib.stream_ptr(rows.device)
     bias_ptr = None if bias is None else bias.data_ptr()
+    try:
+        flags = _lib.FLAG_STATIC_WEIGHTS | {"auto": 0, "epilogue": _lib.FLAG_GATHER_EPILOGUE,
+                                            "push": _lib.FLAG_GATHER_PUSH}[form]
+    except KeyError:
+        raise ValueError(f"form must be auto, epilogue or push; got {form!r}") from None
     with torch.cuda.device(rows.device):
         if is_w4:
             layout = _lib.W4_REF_SPLIT_HALF_SYM if zeros is None else _lib.W4_ASYM_ZP_INT32
@@ -111,7 +122,7 @@ def fused_forward_gather(rows: torch.Tensor, out: SymmetricOutput, *, qweight=No
                 packed.data_ptr(), packed.stride(0) * packed.element_size(), layout,
                 scales.data_ptr(), None if zeros is None else zeros.data_ptr(), group_size, bias_ptr,
                 ctypes.byref(out.desc), out.tensor.stride(0), m, n_local, k,
-                ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                ws.data_ptr(), ws.numel(), flags, stream),
                 "b200q_w4a16_forward_gather")
         else:
             _lib.check(lib.b200q_w8a16_forward_gather(
@@ -119,7 +130,7 @@ def fused_forward_gather(rows: torch.Tensor, out: SymmetricOutput, *, qweight=No
                 qweight.data_ptr(), qweight.stride(0), scales.data_ptr(),
                 _lib.dtype_enum(scales.dtype), bias_ptr,
                 ctypes.byref(out.desc), out.tensor.stride(0), m, n_local, k,
-                ws.data_ptr(), ws.numel(), _lib.FLAG_STATIC_WEIGHTS, stream),
+                ws.data_ptr(), ws.numel(), flags, stream),
                 "b200q_w8a16_forward_gather")
         _lib.check(lib.b200q_gather_wait(ctypes.byref(out.desc), tiles, stream), "b200q_gather_wait")
     return True
@@ -128,22 +139,26 @@ def fused_forward_gather(rows: torch.Tensor, out: SymmetricOutput, *, qweight=No
 class ColumnParallelLinear(nn.Module):
     """This rank's shard plus the all-gather that rebuilds ``[..., N]`` on every rank.
 
-    ``fused=True`` (CUDA, NVLink peers) replaces "kernel, then NCCL all-gather" by one kernel
-    whose epilogue stores each finished tile straight into every rank's output buffer through
-    peer-mapped pointers, followed by a tiny wait kernel.  The output is then a persistent
+    ``fused=True`` (CUDA, NVLink peers) replaces "kernel, then NCCL all-gather" by this library's
+    own exchange over peer-mapped pointers: the forward writes this rank's columns into its own
+    buffer and a push kernel copies them into every peer's, or the forward kernel's epilogue stores
+    each finished tile into every rank's buffer (``gather_form``: "auto" picks by geometry, "push",
+    "epilogue"); a tiny wait kernel holds the stream until every rank's columns are here.  The
+    output is then a persistent
     symmetric-memory buffer per row count (returned as is: copy it if you need it beyond the
     next call with the same row count), allocated on first use by a rendezvous that every rank
     must reach, so all ranks must call with the same sequence of shapes.
     """
 
     def __init__(self, local: nn.Module, *, world: int | None = None, group=None,
-                 gather: bool = True, fused: bool = False):
+                 gather: bool = True, fused: bool = False, gather_form: str = "auto"):
         super().__init__()
         self.local = local
         self.group = group
         self.world = world if world is not None else dist.get_world_size(group)
         self.gather = gather
         self.fused = fused
+        self.gather_form = gather_form
         self.in_features = local.in_features
         self.out_features = local.out_features * self.world
         self._buffers_by_rows: dict = {}
@@ -173,9 +188,10 @@ class ColumnParallelLinear(nn.Module):
         bias = None if local.bias is None else local.bias.to(rows.dtype).contiguous()
         if isinstance(local, W4A16Linear):
             done = fused_forward_gather(rows, out, packed=local.packed, scales=local.scales, bias=bias,
-                                        group_size=local.group_size)
+                                        group_size=local.group_size, form=self.gather_form)
         else:
-            done = fused_forward_gather(rows, out, qweight=local.qweight, scales=local.scales, bias=bias)
+            done = fused_forward_gather(rows, out, qweight=local.qweight, scales=local.scales, bias=bias,
+                                        form=self.gather_form)
         return out.tensor.reshape(*x.shape[:-1], self.out_features) if done else None
 
     def gather_status(self) -> int:

@@ -99,6 +99,17 @@ typedef enum b200q_kernel {
  * 8192 rows per call (B200Q_ERR_UNSUPPORTED beyond).  Tensor-core kernel only; not with
  * SWIGLU_PAIRS, not in the *_forward_gather entry points.                                   */
 #define B200Q_FLAG_ARGMAX 0x400
+/*
+ * With the *_forward_gather entry points only: how the output reaches the peers.
+ * EPILOGUE: from the forward kernel's epilogue (every block stores its tile into every rank's
+ * buffer).  PUSH: a plain forward into this rank's own buffer, then a push kernel that copies
+ * the rank's columns to the peers from as many blocks as the slab is worth.  Neither flag: the
+ * library picks by geometry (few large tiles and single-row int8 calls are pushed).  Both forms
+ * count the same b200q_gather_tiles() arrivals and are followed by b200q_gather_wait; every
+ * rank must pass the same flags for a call.
+ */
+#define B200Q_FLAG_GATHER_EPILOGUE 0x800
+#define B200Q_FLAG_GATHER_PUSH 0x1000
 
 /* W8 quantizer flavours */
 typedef enum b200q_w8_mode {
@@ -272,9 +283,10 @@ int b200q_w4a16_forward(const void* x, int64_t ldx, int act_dtype,
  *   signal_peer[r]  peer-mapped base of rank r's signal block: >= 256 bytes, 8-byte
  *                   aligned, zero-filled once when the buffer is created, never
  *                   touched by the host afterwards
- * Protocol per call: the kernel announces "this rank has entered the call" to all
- * ranks, waits (bounded) for the same announcement from a rank before its first
- * store into that rank's buffer, and counts each delivered tile on every rank.
+ * Protocol per call: the rank announces "entered the call" to all ranks, waits (bounded)
+ * for the same announcement from a rank before its first store into that rank's buffer,
+ * and counts its b200q_gather_tiles() delivered tiles on every rank (signal word 3 of a
+ * rank's own block counts the finished blocks of its push kernel and is zero between calls).
  * b200q_gather_wait, enqueued after the forward on the same stream, waits (bounded)
  * until all world * b200q_gather_tiles() tiles have arrived, which makes the full
  * output safe to read by later work in the stream.  Every rank must make the same

@@ -40,34 +40,37 @@ def _worker(rank, world, port, result):
                 # an element may land on the neighbouring bf16 value (one ulp = 2^-8 relative)
                 assert float((out.float() - single.float()).abs().max()) <= \
                     2.0 ** -7 * float(single.float().abs().max())
-            # the same through the fused epilogue (peer stores + wait kernel, no NCCL call)
-            fused = ColumnParallelLinear(shard_quantized_linear(full, rank, world), world=world, fused=True)
-            for m in (1, 16, 64, 512, 16):
-                x = torch.randn(m, 4096, device="cuda", dtype=torch.bfloat16)
+            # the same through this library's own exchange (peer stores + wait kernel, no NCCL
+            # call): chosen by geometry, the push kernel, and the epilogue form
+            for form in ("auto", "push", "epilogue"):
+                fused = ColumnParallelLinear(shard_quantized_linear(full, rank, world), world=world, fused=True,
+                                             gather_form=form)
+                for m in (1, 16, 64, 512, 16):
+                    x = torch.randn(m, 4096, device="cuda", dtype=torch.bfloat16)
+                    dist.broadcast(x, 0)
+                    single = full(x)
+                    for _ in range(3):                      # back-to-back reuse of the same buffer
+                        out = fused(x)
+                    torch.cuda.synchronize()
+                    assert out.shape == single.shape
+                    assert float((out.float() - single.float()).abs().max()) <= \
+                        2.0 ** -7 * float(single.float().abs().max()), (type(full).__name__, m, form)
+                assert fused.gather_status() == 0
+                # and under CUDA-graph replay
+                x = torch.randn(16, 4096, device="cuda", dtype=torch.bfloat16)
                 dist.broadcast(x, 0)
-                single = full(x)
-                for _ in range(3):                      # back-to-back reuse of the same buffer
-                    out = fused(x)
+                fused(x)
                 torch.cuda.synchronize()
-                assert out.shape == single.shape
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out = fused(x)
+                for _ in range(5):
+                    graph.replay()
+                torch.cuda.synchronize()
+                single = full(x)
                 assert float((out.float() - single.float()).abs().max()) <= \
-                    2.0 ** -7 * float(single.float().abs().max()), (type(full).__name__, m)
-            assert fused.gather_status() == 0
-            # and under CUDA-graph replay
-            x = torch.randn(16, 4096, device="cuda", dtype=torch.bfloat16)
-            dist.broadcast(x, 0)
-            fused(x)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out = fused(x)
-            for _ in range(5):
-                graph.replay()
-            torch.cuda.synchronize()
-            single = full(x)
-            assert float((out.float() - single.float()).abs().max()) <= \
-                2.0 ** -7 * float(single.float().abs().max())
-            assert fused.gather_status() == 0
+                    2.0 ** -7 * float(single.float().abs().max())
+                assert fused.gather_status() == 0
         result[rank] = 1
     finally:
         dist.destroy_process_group()
