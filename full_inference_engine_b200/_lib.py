@@ -75,6 +75,7 @@ class Gather(ctypes.Structure):
 _gather_p = ctypes.POINTER(Gather)
 _SIGNATURES.update({
     "b200q_gather_tiles": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int]),
+    "b200q_gather_form": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "b200q_w4a16_forward_gather": (_c_int, [_c_void_p, _c_i64, _c_int, _c_void_p, _c_i64, _c_int, _c_void_p,
                                             _c_void_p, _c_int, _c_void_p, _gather_p, _c_i64, _c_int, _c_int,
                                             _c_int, _c_void_p, _c_size, _c_int, _c_void_p]),

@@ -73,16 +73,21 @@ static int run_forward(ForwardArgs& a, int kernel_and_flags) {
 // Measured on 2 and 4 GPUs (B200, NVLink): push wins at M = 256..512 with N_local <= 3072
 // (28 against 34 us, 34 against 41 us) and for the single-row int8 GEMV, the epilogue everywhere
 // else.  B200Q_FLAG_GATHER_EPILOGUE / B200Q_FLAG_GATHER_PUSH force one form.
-static bool gather_by_push(const ForwardArgs& a, const b200q_gather* g, int flags) {
-  if (g->world < 2 || a.N % 8 || a.ldy % 8) return false;       // the push moves whole 16-byte chunks
-  for (int r = 0; r < g->world; ++r)
-    if (reinterpret_cast<uintptr_t>(g->y_peer[r]) % 16) return false;
+static bool push_preferred(int format, int M, int n_local, int K, int world, int flags) {
+  if (world < 2 || n_local % 8) return false;                   // the push moves whole 16-byte chunks
   if (flags & B200Q_FLAG_GATHER_EPILOGUE) return false;
   if (flags & B200Q_FLAG_GATHER_PUSH) return true;
-  if (a.format == FMT_W8 && a.M <= kSimtMaxRowsW8) return true;  // the CUDA-core kernel has no gather epilogue
-  const int tiles = tc_output_tiles(a.format, a.M, a.N, a.K);
-  const long long per_block = static_cast<long long>(tc_tile_bytes(a.format, a.M, a.N, a.K)) * (g->world - 1);
+  if (format == FMT_W8 && M <= kSimtMaxRowsW8) return true;      // the CUDA-core kernel has no gather epilogue
+  const int tiles = tc_output_tiles(format, M, n_local, K);
+  const long long per_block = static_cast<long long>(tc_tile_bytes(format, M, n_local, K)) * (world - 1);
   return tiles > 0 && tiles <= 32 && per_block >= 96 * 1024;
+}
+
+static bool gather_by_push(const ForwardArgs& a, const b200q_gather* g, int flags) {
+  if (a.ldy % 8) return false;
+  for (int r = 0; r < g->world; ++r)
+    if (reinterpret_cast<uintptr_t>(g->y_peer[r]) % 16) return false;
+  return push_preferred(a.format, a.M, a.N, a.K, g->world, flags);
 }
 
 static int forward_then_push(ForwardArgs& a, const b200q_gather* g, int tiles, int flags) {
@@ -280,6 +285,11 @@ int b200q_gather_tiles(int format, int M, int N_local, int K, int group) {
   if (format == 8) return (K % 64 == 0) ? tc_output_tiles(FMT_W8, M, N_local, K) : 0;
   if (format == 4) return (group == 128 && K % 128 == 0) ? tc_output_tiles(FMT_W4_REF, M, N_local, K) : 0;
   return 0;
+}
+
+int b200q_gather_form(int format, int M, int N_local, int K, int group, int world, int flags) {
+  if (b200q_gather_tiles(format, M, N_local, K, group) <= 0 || world < 1 || world > 8) return -1;
+  return push_preferred(format == 8 ? FMT_W8 : FMT_W4_REF, M, N_local, K, world, flags) ? 1 : 0;
 }
 
 int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype, const void* packed,

@@ -305,6 +305,11 @@ typedef struct b200q_gather {
 /* Output tiles one rank's forward of this geometry delivers (0: not supported fused). */
 int b200q_gather_tiles(int format, int M, int N_local, int K, int group);
 
+/* Which form such a call takes for 16-byte aligned buffers: 0 the forward's epilogue, 1 the push
+ * kernel, -1 not supported.  A function of the geometry, the world size and the GATHER flags
+ * only, so every rank answers alike. */
+int b200q_gather_form(int format, int M, int N_local, int K, int group, int world, int flags);
+
 int b200q_w4a16_forward_gather(const void* x, int64_t ldx, int act_dtype,
                                const void* packed, int64_t ldw, int layout,
                                const void* scales, const void* zeros, int group,

@@ -80,3 +80,21 @@ def test_gathered_output_equals_single_process_output(world):
     result = mp.get_context("spawn").Manager().dict()
     mp.spawn(_worker, args=(world, port, result), nprocs=world, join=True)
     assert sorted(result.keys()) == list(range(world))
+
+
+def test_gather_form_is_a_function_of_the_geometry_only():
+    """Every rank must pick the same way to deliver its columns (the forms count arrivals alike
+    but launch different kernels): few large tiles and single-row int8 calls are pushed."""
+    from full_inference_engine_b200 import _lib
+
+    lib = _lib.library()
+    form = lambda fmt, m, n_local, k, world, flags=0: lib.b200q_gather_form(fmt, m, n_local, k, 128, world, flags)
+    assert form(8, 512, 512, 4096, 8) == 1                 # 16 tiles of 32 KiB x 7 peers
+    assert form(4, 256, 1536, 4096, 8) == 1                # 12 tiles of 64 KiB x 7 peers
+    assert form(4, 4096, 1536, 4096, 8) == 0               # hundreds of tiles: the epilogue hides the stores
+    assert form(4, 16, 1536, 4096, 8) == 0                 # small tiles
+    assert form(8, 1, 2048, 4096, 2) == 1                  # the int8 GEMV has no gather epilogue
+    assert form(8, 512, 2048, 4096, 2) == 0                # one peer: a tile never reaches 96 KiB
+    assert form(8, 512, 512, 4096, 8, _lib.FLAG_GATHER_EPILOGUE) == 0
+    assert form(4, 16, 1536, 4096, 8, _lib.FLAG_GATHER_PUSH) == 1
+    assert form(4, 16, 1536, 4000, 8) == -1                # the tensor-core kernels do not take this K
