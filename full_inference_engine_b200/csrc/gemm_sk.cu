@@ -316,11 +316,21 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // One thread, and every instruction of it is on the block's critical path (a dependent
+    // scalar sequence issues one instruction every several cycles beside the dequantise warps'
+    // bursts): descriptors and ring positions advance incrementally, a segment is counted down.
     if (elect_one()) {
       bool ok = true;
-      int sx = 0, as = 0, kb = kbi0;
+      int sx = 0, as = 0;
       uint32_t x_phase = 0, a_phase = 0, acc_phase = 1;   // acc_phase: parity to wait for on acc_empty
+      int seg_left = min(KB - kbi0, n_units);             // units left in the current segment (tile)
+      int after_seg = n_units - seg_left;                 // units after it
       bool seg_first = true;
+      const uint64_t x_desc0 = umma_desc_sw128(x_ring);
+      const uint64_t x_step = static_cast<uint64_t>(x_bytes >> 4), atom_step = static_cast<uint64_t>(x_atom_bytes >> 4);
+      uint64_t x_desc = x_desc0;
+      const uint32_t a_tmem0 = tmem_base + kSkACol0;
+      uint32_t a_tmem = a_tmem0;
       for (int i = 0; i < n_units; ++i) {
         if (seg_first) {
           // the epilogue has read the previous segment out of the accumulator
@@ -331,31 +341,32 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         ok = wait_or_abort(x_full + 8 * sx, x_phase, abort_p) && wait_or_abort(a_full + 8 * as, a_phase, abort_p);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t x_stage = x_ring + sx * x_bytes;
+        // operand stage `as` holds 128 K elements as 64 columns, 8 per MMA; two 64-K atoms of activations
+        umma_f16_ts(tmem_base, a_tmem, x_desc, p.idesc, seg_first ? 0u : 1u);
 #pragma unroll
-        for (int atom = 0; atom < 2; ++atom) {
-          const uint64_t bdesc = umma_desc_sw128(x_stage + atom * x_atom_bytes);
-          // operand stage `as` holds 128 K elements as 64 columns, 8 per MMA
-          const uint32_t a_tmem = tmem_base + kSkACol0 + as * 64 + atom * 32;
+        for (int k = 1; k < 4; ++k) umma_f16_ts(tmem_base, a_tmem + 8 * k, x_desc + 2 * k, p.idesc, 1u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t acc = (!seg_first || atom > 0 || k > 0) ? 1u : 0u;
-            umma_f16_ts(tmem_base, a_tmem + 8 * k, bdesc + 2 * k, p.idesc, acc);
-          }
-        }
+        for (int k = 0; k < 4; ++k)
+          umma_f16_ts(tmem_base, a_tmem + 32 + 8 * k, x_desc + atom_step + 2 * k, p.idesc, 1u);
         umma_commit(a_empty + 8 * as);
         umma_commit(x_empty + 8 * sx);
-        const bool seg_last = (kb == KB - 1) || (i == n_units - 1);
-        if (seg_last) umma_commit(acc_full);
-        seg_first = seg_last;
-        if (++kb == KB) kb = 0;
+        seg_first = --seg_left == 0;
+        if (seg_first) {
+          umma_commit(acc_full);
+          seg_left = min(KB, after_seg);
+          after_seg -= seg_left;
+        }
+        x_desc += x_step;
         if (++sx == p.x_stages) {
           sx = 0;
           x_phase ^= 1;
+          x_desc = x_desc0;
         }
+        a_tmem += 64;
         if (++as == kSkAStages) {
           as = 0;
           a_phase ^= 1;
+          a_tmem = a_tmem0;
         }
       }
       if (!ok) flag_failure(abort_p, p.status, 2u);
