@@ -98,3 +98,16 @@ def test_gather_form_is_a_function_of_the_geometry_only():
     assert form(8, 512, 512, 4096, 8, _lib.FLAG_GATHER_EPILOGUE) == 0
     assert form(4, 16, 1536, 4096, 8, _lib.FLAG_GATHER_PUSH) == 1
     assert form(4, 16, 1536, 4000, 8) == -1                # the tensor-core kernels do not take this K
+
+
+def test_column_parallel_module_carries_the_gather_form():
+    """The form is part of the module's configuration (every rank must build it alike) and is
+    validated where it is used, not silently ignored."""
+    from full_inference_engine_b200.quantization.sharded import ColumnParallelLinear, fused_forward_gather
+
+    local = W4A16Linear(256, 128)
+    for form in ("auto", "push", "epilogue"):
+        assert ColumnParallelLinear(local, world=2, fused=True, gather_form=form).gather_form == form
+    assert ColumnParallelLinear(local, world=2).gather_form == "auto"
+    import inspect
+    assert inspect.signature(fused_forward_gather).parameters["form"].default == "auto"
